@@ -93,16 +93,21 @@ class SequenceSlots:
 
     ``windows[g]`` is ``None`` for a group that keeps every key, or the number
     of latest keys a windowed group needs; a windowed group gives pages back as
-    soon as no later query can see them.
+    soon as no later query can see them.  ``chunks[g]`` is ``None`` or the
+    number of positions in a chunk of a group whose queries see only keys of
+    their own chunk (chunks counted from position 0); such a group gives back
+    the pages that lie wholly before the chunk the sequence has reached.
     """
 
     def __init__(self, max_seqs: int, pools: Sequence[PagePool],
-                 windows: Optional[Sequence[Optional[int]]] = None):
+                 windows: Optional[Sequence[Optional[int]]] = None,
+                 chunks: Optional[Sequence[Optional[int]]] = None):
         self.max_seqs = max_seqs
         self.pools = list(pools)
         self.windows = list(windows) if windows is not None else [None] * len(self.pools)
-        if len(self.windows) != len(self.pools):
-            raise ValueError("one window entry per pool")
+        self.chunks = list(chunks) if chunks is not None else [None] * len(self.pools)
+        if len(self.windows) != len(self.pools) or len(self.chunks) != len(self.pools):
+            raise ValueError("one window entry and one chunk entry per pool")
         self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
         self._len: Dict[int, int] = {}
         self._pages: Dict[int, List[GroupPages]] = {}
@@ -187,14 +192,21 @@ class SequenceSlots:
             if pages_for(new_len) > len(gp.table):
                 raise SlotError(f"slot {slot}: advanced to {new_len} tokens without reserved pages")
         self._len[slot] = new_len
-        for pool, gp, w in zip(self.pools, self._pages[slot], self.windows):
-            if w is None:
+        for pool, gp, w, ch in zip(self.pools, self._pages[slot], self.windows, self.chunks):
+            if w is None and ch is None:
                 continue
             # a later query sits at position >= new_len and sees keys > position - w,
-            # so key j is dead once j <= new_len - w; page i holds keys up to i*P + P-1
+            # so key j is dead once j <= new_len - w; page i holds keys up to i*P + P-1.
+            # With chunks it sees no key before its chunk's first position, which is at least
+            # that of position new_len's chunk.
+            last_dead = -1
+            if w is not None:
+                last_dead = new_len - w
+            if ch is not None:
+                last_dead = max(last_dead, (new_len // ch) * ch - 1)
             i = gp.released
             dead = []
-            while i < len(gp.table) and i * PAGE_TOKENS + PAGE_TOKENS - 1 <= new_len - w:
+            while i < len(gp.table) and i * PAGE_TOKENS + PAGE_TOKENS - 1 <= last_dead:
                 if gp.table[i] >= 0:
                     dead.append(gp.table[i])
                     gp.table[i] = -1

@@ -9,6 +9,10 @@ each group storage of its own:
   for V.  Groups that keep all keys and groups that keep a window of them have
   separate page pools, and a windowed group gives pages back while the
   sequence is still running.
+  ``v_head_dim`` gives values a size of their own (``None``: the keys' size).
+  ``chunk`` says that a query sees only keys of its own chunk of that many
+  positions (chunks counted from position 0): such a group gives a page back
+  once every key in it lies before the chunk the sequence has reached.
 * ``StateRequest(shape, dtype)``: state of fixed size per sequence,
   ``[max_seqs + 1, *shape]`` per entry, zeroed when a slot is opened.  The last
   row belongs to no sequence (``Cache.spare_slot``): rows that pad a step up to
@@ -18,6 +22,9 @@ each group storage of its own:
   The Qwen3 dense decoder has no such state; it exists for mixers that carry a
   running state (the reference's GatedDeltaNetState, model.rs:377-492, is such
   a thing).
+* ``BundleRequest(items)``: several of the above for ONE cache entry (a layer
+  whose mixer holds keys and a running state, with the last inputs of a short
+  convolution beside them); the entry's view is the tuple of the items' views.
 
 The reference's equivalent is ``KvCache``/``LayerCache``
 (crates/synaptix-models/llm/common/src/model.rs:349-368,1021-1046).
@@ -37,6 +44,12 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclasses.dataclass(frozen=True)
@@ -45,7 +58,12 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
-CacheRequest = Union[KVRequest, StateRequest, None]
+@dataclasses.dataclass(frozen=True)
+class BundleRequest:
+    items: tuple          # of KVRequest, StateRequest, BundleRequest or None
+
+
+CacheRequest = Union[KVRequest, StateRequest, BundleRequest, None]
 
 
 class KVView:
@@ -54,7 +72,7 @@ class KVView:
 
     def __init__(self, k: torch.Tensor, v: torch.Tensor, group: int, window: Optional[int]):
         self.k = k          # [n_pages, n_kv_heads, PAGE_TOKENS, head_dim]
-        self.v = v
+        self.v = v          # [n_pages, n_kv_heads, PAGE_TOKENS, value_dim]
         self.group = group  # index of the block table to use (StepContext.block_tables[group])
         self.window = window
 
@@ -75,39 +93,44 @@ class Cache:
             raise ValueError("max_seqs must be > 0")
 
         # group equal requests
-        self._entry: List[Optional[Tuple[str, int, int]]] = []   # (kind, group, index in group)
+        self._entry: List = []   # per entry: None, (kind, group, index in group), or a list of those for a bundle
         kv_keys: List[KVRequest] = []
         kv_counts: List[int] = []
         st_keys: List[StateRequest] = []
         st_counts: List[int] = []
-        for r in requests:
+
+        def place(r):
             if r is None:
-                self._entry.append(None)
-            elif isinstance(r, KVRequest):
+                return None
+            if isinstance(r, KVRequest):
                 if r not in kv_keys:
                     kv_keys.append(r)
                     kv_counts.append(0)
                 g = kv_keys.index(r)
-                self._entry.append(("kv", g, kv_counts[g]))
                 kv_counts[g] += 1
-            elif isinstance(r, StateRequest):
+                return ("kv", g, kv_counts[g] - 1)
+            if isinstance(r, StateRequest):
                 if r not in st_keys:
                     st_keys.append(r)
                     st_counts.append(0)
                 g = st_keys.index(r)
-                self._entry.append(("state", g, st_counts[g]))
                 st_counts[g] += 1
-            else:
-                raise TypeError(f"not a cache request: {r!r}")
+                return ("state", g, st_counts[g] - 1)
+            if isinstance(r, BundleRequest):        # bundles may hold bundles (a block's, with its mixer's inside)
+                return [place(i) for i in r.items]
+            raise TypeError(f"not a cache request: {r!r}")
+
+        for r in requests:
+            self._entry.append(place(r))
         self.kv_groups = kv_keys
         self.state_groups = st_keys
 
         self._k: List[torch.Tensor] = []
         self._v: List[torch.Tensor] = []
         for r, n in zip(kv_keys, kv_counts):
-            shape = (n, self.n_pages, r.n_kv_heads, PAGE_TOKENS, r.head_dim)
-            self._k.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self._v.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            shape = (n, self.n_pages, r.n_kv_heads, PAGE_TOKENS)
+            self._k.append(torch.zeros(shape + (r.head_dim,), dtype=dtype, device=self.device))
+            self._v.append(torch.zeros(shape + (r.value_dim,), dtype=dtype, device=self.device))
         self._state: List[torch.Tensor] = []
         for r, n in zip(st_keys, st_counts):
             self._state.append(torch.zeros((n, self.max_seqs + 1) + tuple(r.shape),
@@ -119,13 +142,14 @@ class Cache:
             windows: List[Optional[int]] = [None]
         else:
             windows = [r.window for r in kv_keys]
-        self.slots = SequenceSlots(self.max_seqs, pools, windows)
+        chunks = [r.chunk for r in kv_keys] if kv_keys else [None]
+        self.slots = SequenceSlots(self.max_seqs, pools, windows, chunks)
 
     @property
     def kv_bytes_per_token(self) -> int:
         """Bytes of keys and values one cached token takes over all layers (the reference's figure of that name,
         crates/synaptix-models/llm/common/src/model.rs:932-954): 147,456 for the Qwen3-4B shape in bfloat16."""
-        return sum(2 * k.shape[0] * k.shape[2] * k.shape[4] * k.element_size() for k in self._k)
+        return sum(t.shape[0] * t.shape[2] * t.shape[4] * t.element_size() for t in self._k + self._v)
 
     # -- views ------------------------------------------------------------
     @property
@@ -138,9 +162,13 @@ class Cache:
         return self.max_seqs
 
     def view(self, entry: int):
-        e = self._entry[entry]
+        return self._view_of(self._entry[entry])
+
+    def _view_of(self, e):
         if e is None:
             return None
+        if isinstance(e, list):
+            return tuple(self._view_of(i) for i in e)
         kind, g, i = e
         if kind == "kv":
             return KVView(self._k[g][i], self._v[g][i], g, self.kv_groups[g].window)

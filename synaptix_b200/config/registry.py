@@ -2,7 +2,8 @@
 
 The reference picks the architecture from ``config.json``'s ``model_type`` with
 Qwen3 as the default arm (crates/synaptix/src/facade/arch.rs:62-83).  Here the
-lookup is explicit: ``architectures[0]`` first, then ``model_type``; an unknown
+lookup is explicit: ``architectures[0]`` (or the single name under
+``architecture``) first, then ``model_type``; an unknown
 name is an error that lists what is registered.
 
 A builder is ``build(config, weights, runtime) -> Model`` (see
@@ -46,6 +47,8 @@ def registered_architectures() -> List[str]:
 def resolve_architecture(config_dict: Dict[str, Any]) -> ArchitectureEntry:
     """Find the registered architecture a parsed config.json asks for."""
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):     # one name under the singular key
+        archs = [config_dict["architecture"]]
     if isinstance(archs, list):
         for a in archs:
             if a in _BY_ARCH:

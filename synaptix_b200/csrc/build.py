@@ -39,6 +39,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 LIBRARIES: Dict[str, tuple] = {
     "generic": ("generic.cu", []),
     "sampling": ("sampling.cu", []),
+    "sequence": ("sequence.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
     "attn_decode": ("attn_decode.cu", []),

@@ -288,12 +288,11 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
     const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq,
     int rotary_dim, float eps, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-    const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, int n_pages) {
+    const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, int n_pages, int row, int vd) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[t];
-  const int row = (nh + 2 * nkv) * hd;
   const T* src_tok = qkv + (size_t)t * row;
   const int half = inv_freq ? rotary_dim / 2 : 0;
 
@@ -313,25 +312,27 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
   const int s = seq_of_token[t];
   const int page = block_table[(size_t)s * maxp + (pos >> 6)];
   const bool page_ok = page >= 0 && page < n_pages;     // the host guarantees a page; never write outside
-  const bool vec_copy = (hd % 8 == 0) && sizeof(T) == 2;
+  const bool vec_copy = (vd % 8 == 0) && (row % 8 == 0) && ((nh + nkv) * hd % 8 == 0) && sizeof(T) == 2 &&
+                        (((uintptr_t)qkv | (uintptr_t)v_pages) & 15) == 0;
 
   for (int head = blockIdx.y * QP_WARPS + warp; head < nh + 2 * nkv; head += gridDim.y * QP_WARPS) {
     const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
     const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
-    const T* src = src_tok + (size_t)head * hd;
+    // value heads have a size of their own (vd) and follow the nh + nkv heads of size hd
+    const T* src = (is_q || is_k) ? src_tok + (size_t)head * hd : src_tok + (size_t)(nh + nkv) * hd + (size_t)kvh * vd;
     T* dst;
     if (is_q) {
       dst = q_out + ((size_t)t * nh + head) * hd;
     } else {
       T* base = is_k ? k_pages : v_pages;
       if (!base || !page_ok) continue;                   // a layer that reads another layer's cache writes nothing
-      dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * hd;
+      dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * (is_k ? hd : vd);
     }
     if (!is_q && !is_k) {                                // v: copy
       if (vec_copy) {
-        for (int i = lane; i < hd / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        for (int i = lane; i < vd / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
       } else {
-        for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+        for (int i = lane; i < vd; i += 32) dst[i] = src[i];
       }
       continue;
     }
@@ -564,10 +565,11 @@ template <typename T>
 static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, void* q_out, void* k_pages, void* v_pages,
                               const float* wq, const float* wk, const float* inv_freq, int rotary_dim, float eps,
                               const int* positions, const int* seq_of_token, const int* block_table, int maxp, int nh,
-                              int nkv, int hd, int n_pages) {
+                              int nkv, int hd, int n_pages, int row, int vd) {
   const int pairs = inv_freq ? rotary_dim / 2 : 0;
+  const bool packed = row == (nh + 2 * nkv) * hd && vd == hd;      // the layout the two faster kernels assume
   const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 7) == 0;
-  if (sizeof(T) == 2 && (hd == 128 || hd == 64) && (!inv_freq || rotary_dim == hd) && grid.y == 1 &&
+  if (packed && sizeof(T) == 2 && (hd == 128 || hd == 64) && (!inv_freq || rotary_dim == hd) && grid.y == 1 &&
       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0) {
 #define QP_WGO(HD)                                                                                                       \
   return sx_launch(qkv_prepare_wide_kernel<HD>, grid, dim3(QP_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out,      \
@@ -577,7 +579,7 @@ static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, v
     QP_WGO(64);
 #undef QP_WGO
   }
-  if (hd % 4 == 0 && hd <= 512 && aligned && (!inv_freq || rotary_dim == hd)) {
+  if (packed && hd % 4 == 0 && hd <= 512 && aligned && (!inv_freq || rotary_dim == hd)) {
 #define QP_VGO(PQ)                                                                                                     \
   return sx_launch(qkv_prepare_vec_kernel<T, PQ>, grid, dim3(QP_WARPS * 32), 0, stream, (const T*)qkv, (T*)q_out, (T*)k_pages, \
                    (T*)v_pages, wq, wk, inv_freq, eps, positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages)
@@ -588,7 +590,7 @@ static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, v
   }
 #define QP_GO(PP)                                                                                                   \
   return sx_launch(qkv_prepare_kernel<T, PP>, grid, dim3(QP_WARPS * 32), 0, stream, (const T*)qkv, (T*)q_out, (T*)k_pages, \
-                   (T*)v_pages, wq, wk, inv_freq, rotary_dim, eps, positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages)
+                   (T*)v_pages, wq, wk, inv_freq, rotary_dim, eps, positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages, row, vd)
   if (pairs <= 32) QP_GO(1);
   else if (pairs <= 64) QP_GO(2);
   else if (pairs <= 128) QP_GO(4);
@@ -596,23 +598,44 @@ static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, v
 #undef QP_GO
 }
 
-extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void* v_pages,
+static int qkv_prepare_any(const void* qkv, void* q_out, void* k_pages, void* v_pages,
                               const float* wq, const float* wk, const float* inv_freq, int rotary_dim,
                               float eps, const int* positions, const int* seq_of_token,
                               const int* block_table, int maxp, int n_tokens, int nh, int nkv, int hd,
-                              int n_pages, int dt, cudaStream_t stream) {
+                              int n_pages, int dt, int row, int vd, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || (rotary_dim & 1) || rotary_dim > hd || rotary_dim / 2 > 32 * QP_MAXP) return SX_ERR_SIZE;
+  if (vd <= 0 || row < (nh + nkv) * hd + nkv * vd) return SX_ERR_SIZE;
   // few tokens: spread the heads over blocks too, so that the step is one round of work
   const int heads = nh + 2 * nkv;
   dim3 grid(n_tokens, n_tokens <= 64 ? (heads + QP_WARPS - 1) / QP_WARPS : 1);
   if (dt == SX_F32)
     return qkv_prepare_launch<float>(grid, stream, qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, rotary_dim, eps, positions,
-                                     seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
+                                     seq_of_token, block_table, maxp, nh, nkv, hd, n_pages, row, vd);
   if (dt == SX_BF16)
     return qkv_prepare_launch<bf16>(grid, stream, qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, rotary_dim, eps, positions,
-                                    seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
+                                    seq_of_token, block_table, maxp, nh, nkv, hd, n_pages, row, vd);
   return SX_ERR_DTYPE;
+}
+
+extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void* v_pages,
+                              const float* wq, const float* wk, const float* inv_freq, int rotary_dim,
+                              float eps, const int* positions, const int* seq_of_token,
+                              const int* block_table, int maxp, int n_tokens, int nh, int nkv, int hd,
+                              int n_pages, int dt, cudaStream_t stream) {
+  return qkv_prepare_any(qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, rotary_dim, eps, positions, seq_of_token, block_table,
+                         maxp, n_tokens, nh, nkv, hd, n_pages, dt, (nh + 2 * nkv) * hd, hd, stream);
+}
+
+// The same for a projection whose rows are `row` elements long (q heads, k heads and v heads first, other columns
+// behind them) and whose value heads have `vd` elements.
+extern "C" int sx_qkv_prepare_strided(const void* qkv, void* q_out, void* k_pages, void* v_pages,
+                                      const float* wq, const float* wk, const float* inv_freq, int rotary_dim,
+                                      float eps, const int* positions, const int* seq_of_token,
+                                      const int* block_table, int maxp, int n_tokens, int nh, int nkv, int hd,
+                                      int n_pages, int dt, int row, int vd, cudaStream_t stream) {
+  return qkv_prepare_any(qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, rotary_dim, eps, positions, seq_of_token, block_table,
+                         maxp, n_tokens, nh, nkv, hd, n_pages, dt, row, vd, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -642,13 +665,19 @@ extern "C" int sx_rope_table(const int* positions, const float* inv_freq, int pa
 // ---------------------------------------------------------------------------------------
 // attention over the paged cache, one block per (token, query head): scores of the keys
 // lo..pos in tiles of 128, running maximum and sum (online softmax), all in 32-bit.
-//   lo = window > 0 ? max(0, pos - window + 1) : 0;  query head h reads kv head h / (nh/nkv).
+//   lo = window > 0 ? max(0, pos - window + 1) : 0, and with chunk > 0 at least (pos / chunk) * chunk: a query then
+//   sees only keys of its own chunk of positions;  query head h reads kv head h / (nh/nkv).
+//   softcap > 0: score <- softcap * tanh(score / softcap) after the scale.
+//   sinks: one number per query head that stands in the softmax's denominator as exp(sink) beside the keys' terms
+//   (no key, no value, neither scaled nor capped): the running maximum starts at the sink and the running sum at 1.
+//   Keys have hd elements, values vd; the result goes to out[t * out_stride + h * vd + d], times out_scale.
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128) attn_generic_kernel(
     const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-    const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, float scale, int window) {
+    const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, float scale, int window,
+    int vd, float softcap, const float* __restrict__ sinks, int chunk, int out_stride, float out_scale) {
   extern __shared__ float smem[];
   float* qs = smem;            // hd
   float* ps = smem + hd;       // 128
@@ -661,9 +690,10 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(
   for (int i = tid; i < hd; i += 128) qs[i] = to_f32(qr[i]);
   __syncthreads();
 
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  float m = -INFINITY, l = 0.f;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};     // hd <= 512
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+  float m = sinks ? sinks[h] : -INFINITY, l = sinks ? 1.f : 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};     // vd <= 512
 
   for (int j0 = lo; j0 <= pos; j0 += 128) {
     const int j = j0 + tid;
@@ -674,6 +704,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(
       float d = 0.f;
       for (int i = 0; i < hd; ++i) d = fmaf(qs[i], to_f32(kr[i]), d);
       s = d * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float tmax = block_max(s, red);
     const float m_new = fmaxf(m, tmax);
@@ -686,12 +717,12 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
       const int d = tid + a * 128;
-      if (d < hd) {
+      if (d < vd) {
         float v = acc[a] * corr;
         for (int jj = 0; jj < ntile; ++jj) {
           const int jk = j0 + jj;
           const int page = bt[jk >> 6];
-          v = fmaf(ps[jj], to_f32(v_pages[(((size_t)page * nkv + kvh) * SX_PAGE + (jk & 63)) * hd + d]), v);
+          v = fmaf(ps[jj], to_f32(v_pages[(((size_t)page * nkv + kvh) * SX_PAGE + (jk & 63)) * vd + d]), v);
         }
         acc[a] = v;
       }
@@ -699,33 +730,53 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(
     m = m_new;
     __syncthreads();
   }
-  T* o = out + ((size_t)t * nh + h) * hd;
+  T* o = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
     const int d = tid + a * 128;
-    if (d < hd) o[d] = from_f32<T>(acc[a] / l);
+    if (d < vd) o[d] = from_f32<T>(acc[a] / l * out_scale);
   }
+}
+
+static int attn_generic_any(const void* q, const void* k_pages, const void* v_pages, void* out,
+                            const int* positions, const int* seq_of_token, const int* block_table,
+                            int maxp, int n_tokens, int nh, int nkv, int hd, float scale, int window,
+                            int dt, int vd, float softcap, const float* sinks, int chunk, int out_stride, float out_scale,
+                            cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hd <= 0 || hd > 512 || vd <= 0 || vd > 512 || nkv <= 0 || nh % nkv != 0 || nh > 65535 || out_stride < nh * vd)
+    return SX_ERR_SIZE;
+  dim3 grid(n_tokens, nh);
+  const size_t smem = (size_t)(hd + 128) * sizeof(float);
+  if (dt == SX_F32)
+    attn_generic_kernel<float><<<grid, 128, smem, stream>>>(
+        (const float*)q, (const float*)k_pages, (const float*)v_pages, (float*)out, positions, seq_of_token,
+        block_table, maxp, nh, nkv, hd, scale, window, vd, softcap, sinks, chunk, out_stride, out_scale);
+  else if (dt == SX_BF16)
+    attn_generic_kernel<bf16><<<grid, 128, smem, stream>>>(
+        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, positions, seq_of_token,
+        block_table, maxp, nh, nkv, hd, scale, window, vd, softcap, sinks, chunk, out_stride, out_scale);
+  else
+    return SX_ERR_DTYPE;
+  return sx_launch_status();
 }
 
 extern "C" int sx_attn_generic(const void* q, const void* k_pages, const void* v_pages, void* out,
                                const int* positions, const int* seq_of_token, const int* block_table,
                                int maxp, int n_tokens, int nh, int nkv, int hd, float scale, int window,
                                int dt, cudaStream_t stream) {
-  if (n_tokens <= 0) return 0;
-  if (hd <= 0 || hd > 512 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return SX_ERR_SIZE;
-  dim3 grid(n_tokens, nh);
-  const size_t smem = (size_t)(hd + 128) * sizeof(float);
-  if (dt == SX_F32)
-    attn_generic_kernel<float><<<grid, 128, smem, stream>>>(
-        (const float*)q, (const float*)k_pages, (const float*)v_pages, (float*)out, positions, seq_of_token,
-        block_table, maxp, nh, nkv, hd, scale, window);
-  else if (dt == SX_BF16)
-    attn_generic_kernel<bf16><<<grid, 128, smem, stream>>>(
-        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, positions, seq_of_token,
-        block_table, maxp, nh, nkv, hd, scale, window);
-  else
-    return SX_ERR_DTYPE;
-  return sx_launch_status();
+  return attn_generic_any(q, k_pages, v_pages, out, positions, seq_of_token, block_table, maxp, n_tokens, nh, nkv, hd, scale,
+                          window, dt, hd, 0.f, nullptr, 0, nh * hd, 1.f, stream);
+}
+
+// with the options the plain entry point leaves out (see the kernel's comment)
+extern "C" int sx_attn_generic_ex(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                  const int* positions, const int* seq_of_token, const int* block_table,
+                                  int maxp, int n_tokens, int nh, int nkv, int hd, float scale, int window,
+                                  int dt, int vd, float softcap, const float* sinks, int chunk, int out_stride,
+                                  float out_scale, cudaStream_t stream) {
+  return attn_generic_any(q, k_pages, v_pages, out, positions, seq_of_token, block_table, maxp, n_tokens, nh, nkv, hd, scale,
+                          window, dt, vd, softcap, sinks, chunk, out_stride, out_scale, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -1,0 +1,481 @@
+// Kernels of parts that carry something from token to token besides keys and values: a short causal convolution
+// over time in front of a sublayer, a gated recurrence per channel (minGRU), linear attention with a fixed decay per
+// head (retention), and the small elementwise steps around them (a capped gated activation, vectors added into the
+// residual stream).  Float32 and bfloat16 storage; positions, norms, gates, decays, states and every sum are 32-bit.
+//
+// Tokens of all sequences of a step are packed into one stream, as everywhere in this package: token t belongs to
+// row s = seq_of_token[t] of the per-sequence arrays, the tokens of s are cu_seqlens[s] .. cu_seqlens[s+1]-1 and stand
+// at positions seq_past[s] .. seq_lens[s]-1.  A state lives in a tensor [slots, ...] in 32-bit, indexed by
+// seq_slots[s]; a slot is zeroed when a sequence opens it.  Nothing here needs a value of the step on the host, so
+// every kernel can be recorded into a CUDA graph.
+#include "common.cuh"
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.f + expf(-x)); }
+
+// ---------------------------------------------------------------------------------------
+// Residual sum + RMSNorm in front of a short convolution.
+//   rows 0..T-1:        v = h[t] (+ delta[t], written back);  y[t] = v * rsqrt(mean(v^2) + eps) * w     (32-bit out)
+//   rows T..T+S*P-1:    y[T + s*P + i] = hist[slot(s)][i]   (P = taps - 1: the last P inputs of the sequence before
+//                       this step, oldest first), so that the convolution reads one buffer and may write hist.
+// ---------------------------------------------------------------------------------------
+template <typename TD>
+__global__ void __launch_bounds__(256) add_rmsnorm_hist_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                                               const float* __restrict__ w, float eps, float* __restrict__ y,
+                                                               const float* __restrict__ hist, const int* __restrict__ seq_slots,
+                                                               int T, int P, int H) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int b = blockIdx.x;
+  if (b >= T) {
+    const int s = (b - T) / P, i = (b - T) % P;
+    const float* src = hist + ((size_t)seq_slots[s] * P + i) * H;
+    float* dst = y + (size_t)b * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = src[c];
+    return;
+  }
+  float* hr = h + (size_t)b * H;
+  const TD* dr = delta ? delta + (size_t)b * H : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = hr[c];
+    if (dr) {
+      v += to_f32(dr[c]);
+      hr[c] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  float* yr = y + (size_t)b * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) yr[c] = hr[c] * inv * w[c];
+}
+
+extern "C" int sx_add_rmsnorm_hist(float* h, const void* delta, int delta_dt, const float* w, float eps, float* y,
+                                   const float* hist, const int* seq_slots, int T, int S, int P, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (P < 0 || H <= 0) return SX_ERR_SIZE;
+  const dim3 grid(T + S * P);
+  if (delta_dt == SX_F32)
+    return sx_launch(add_rmsnorm_hist_kernel<float>, grid, dim3(256), 0, stream, h, (const float*)delta, w, eps, y, hist,
+                     seq_slots, T, P, H);
+  if (delta_dt == SX_BF16)
+    return sx_launch(add_rmsnorm_hist_kernel<bf16>, grid, dim3(256), 0, stream, h, (const bf16*)delta, w, eps, y, hist,
+                     seq_slots, T, P, H);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// Short causal convolution over time on each channel, added to its input:
+//   out[t] = y[t] + sum_{j < taps} cw[c][j] * y_at(position(t) - (taps-1) + j)
+// y is the buffer of the kernel above: an input at a position of this step is a row of the step, an older one a
+// history row (zeros before the sequence's start, since a fresh slot's history is zero).  The block of a sequence's
+// last token of the step writes the new history (the last P inputs, oldest first).
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256) token_conv_kernel(const float* __restrict__ y, const float* __restrict__ cw,
+                                                         TO* __restrict__ out, float* __restrict__ hist,
+                                                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_past,
+                                                         const int* __restrict__ seq_lens, const int* __restrict__ seq_slots,
+                                                         int T, int P, int H) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int s = seq_of_token[t], pos = positions[t];
+  const int start = seq_past[s], t0 = cu_seqlens[s], end = seq_lens[s];
+  const int taps = P + 1;
+  // row of y that holds the input at position p (start - P <= p <= pos)
+  auto row_of = [&](int p) -> size_t { return p >= start ? (size_t)(t0 + (p - start)) : (size_t)(T + s * P + (p - start + P)); };
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float acc = y[(size_t)t * H + c];
+    for (int j = 0; j < taps; ++j) acc = fmaf(cw[(size_t)c * taps + j], y[row_of(pos - P + j) * H + c], acc);
+    out[(size_t)t * H + c] = from_f32<TO>(acc);
+  }
+  if (pos == end - 1) {
+    float* hs = hist + (size_t)seq_slots[s] * P * H;
+    for (int i = 0; i < P; ++i) {
+      const size_t r = row_of(end - P + i);
+      for (int c = threadIdx.x; c < H; c += blockDim.x) hs[(size_t)i * H + c] = y[r * H + c];
+    }
+  }
+}
+
+extern "C" int sx_token_conv(const float* y, const float* cw, void* out, int out_dt, float* hist, const int* positions,
+                             const int* seq_of_token, const int* cu_seqlens, const int* seq_past, const int* seq_lens,
+                             const int* seq_slots, int T, int P, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (P < 0 || H <= 0) return SX_ERR_SIZE;
+  if (out_dt == SX_F32)
+    return sx_launch(token_conv_kernel<float>, dim3(T), dim3(256), 0, stream, y, cw, (float*)out, hist, positions, seq_of_token,
+                     cu_seqlens, seq_past, seq_lens, seq_slots, T, P, H);
+  if (out_dt == SX_BF16)
+    return sx_launch(token_conv_kernel<bf16>, dim3(T), dim3(256), 0, stream, y, cw, (bf16*)out, hist, positions, seq_of_token,
+                     cu_seqlens, seq_past, seq_lens, seq_slots, T, P, H);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// The two kernels above as one, for steps in which every sequence brings ONE token (row t is sequence t):
+// sum, norm, convolution over the history and the history's shift, one block a token.  Rows of up to
+// 256 * NC channels stay in registers.
+// ---------------------------------------------------------------------------------------
+template <typename TD, int NC>
+__global__ void __launch_bounds__(256) norm_conv_step_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                                             const float* __restrict__ w, float eps, const float* __restrict__ cw,
+                                                             TD* __restrict__ out, float* __restrict__ hist,
+                                                             const int* __restrict__ seq_slots, int P, int H) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  float* hr = h + (size_t)t * H;
+  const TD* dr = delta ? delta + (size_t)t * H : nullptr;
+  float v[NC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NC; ++k) {
+    const int c = threadIdx.x + k * 256;
+    v[k] = 0.f;
+    if (c < H) {
+      v[k] = hr[c];
+      if (dr) {
+        v[k] += to_f32(dr[c]);
+        hr[c] = v[k];
+      }
+      ss += v[k] * v[k];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  const int taps = P + 1;
+  float* hs = hist + (size_t)seq_slots[t] * P * H;
+#pragma unroll
+  for (int k = 0; k < NC; ++k) {
+    const int c = threadIdx.x + k * 256;
+    if (c >= H) continue;
+    const float yv = v[k] * inv * w[c];
+    const float* cwc = cw + (size_t)c * taps;
+    float acc = fmaf(cwc[P], yv, yv);
+    float prev = yv;                        // walks the history from the newest entry down, shifting it by one
+    for (int i = P - 1; i >= 0; --i) {
+      const float old = hs[(size_t)i * H + c];
+      acc = fmaf(cwc[i], old, acc);
+      hs[(size_t)i * H + c] = prev;
+      prev = old;
+    }
+    out[(size_t)t * H + c] = from_f32<TD>(acc);
+  }
+}
+
+extern "C" int sx_norm_conv_step(float* h, const void* delta, const float* w, float eps, const float* cw, void* out,
+                                 float* hist, const int* seq_slots, int T, int P, int H, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (P < 0 || H <= 0 || H > 256 * 32) return SX_ERR_SIZE;
+#define NCS_GO(TD, NC)                                                                                              \
+  return sx_launch(norm_conv_step_kernel<TD, NC>, dim3(T), dim3(256), 0, stream, h, (const TD*)delta, w, eps, cw, (TD*)out, \
+                   hist, seq_slots, P, H)
+#define NCS_PICK(TD)              \
+  if (H <= 256 * 4) NCS_GO(TD, 4);  \
+  if (H <= 256 * 8) NCS_GO(TD, 8);  \
+  if (H <= 256 * 16) NCS_GO(TD, 16); \
+  NCS_GO(TD, 32)
+  if (dt == SX_F32) { NCS_PICK(float); }
+  if (dt == SX_BF16) { NCS_PICK(bf16); }
+#undef NCS_PICK
+#undef NCS_GO
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// minGRU: per channel c of N,  z = sigmoid(a_z + b_z),  u = a_x + b_x,  cand = u >= 0 ? u + 1/2 : sigmoid(u),
+//   S <- (1 - z) S + z cand,   out = S * silu(a_g),
+// where a_z, a_x, a_g are columns z_off + c, x_off + c, g_off + c of the projection `proj` [T, row].
+//
+// mingru_scan_kernel walks a sequence's tokens one after the other, a thread a channel: single-token steps and
+// short portions.  Longer portions go through three kernels that cut a sequence's tokens into pieces of CH:
+//   (1) a piece composed from a zero state: (A, B) with S_end = A S_begin + B, per piece and channel;
+//   (2) the pieces' carries one after the other (few), which also leaves the sequence's new state;
+//   (3) every piece again from its true begin state, writing the outputs.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void mingru_gate(const T* __restrict__ row, int z_off, int x_off, int c, float bz, float bx,
+                                            float& keep, float& add) {
+  const float z = sigmoid_f32(to_f32(row[z_off + c]) + bz);
+  const float u = to_f32(row[x_off + c]) + bx;
+  const float cand = u >= 0.f ? u + 0.5f : sigmoid_f32(u);
+  keep = 1.f - z;
+  add = z * cand;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ proj, int row, int z_off, int x_off, int g_off,
+                                                          const float* __restrict__ bz, const float* __restrict__ bx,
+                                                          float* __restrict__ state, T* __restrict__ out,
+                                                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
+                                                          int N) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  const int t0 = cu_seqlens[s], t1 = cu_seqlens[s + 1];
+  float* sp = state + (size_t)seq_slots[s] * N + c;
+  float S = *sp;
+  const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const T* r = proj + (size_t)t * row;
+    float keep, add;
+    mingru_gate(r, z_off, x_off, c, b_z, b_x, keep, add);
+    S = fmaf(keep, S, add);
+    out[(size_t)t * N + c] = from_f32<T>(S * silu_f32(to_f32(r[g_off + c])));
+  }
+  *sp = S;
+}
+
+#define MG_CH 64
+// pieces are counted over the packed stream: piece p covers tokens p*CH .. p*CH+CH-1, cut at sequence borders, so a
+// piece may hold the end of one sequence and the beginning of the next; (A, B) are kept per (piece, part) with part 0
+// = the tokens of the sequence the piece begins in, part 1.. the following sequences (each begins a sequence, so its
+// begin state is that sequence's carried state).  To keep this simple a piece never crosses a border: the host-free
+// way to get that is to cut every SEQUENCE into pieces of its own: piece index = piece_base[s] + k.  piece_base is
+// not known on the device without a scan, so the grid is (max pieces of a sequence, S) and pieces beyond a
+// sequence's end return at once.
+template <typename T>
+__global__ void __launch_bounds__(128) mingru_piece_kernel(const T* __restrict__ proj, int row, int z_off, int x_off,
+                                                           const float* __restrict__ bz, const float* __restrict__ bx,
+                                                           float* __restrict__ AB, const int* __restrict__ cu_seqlens,
+                                                           int N, int max_pieces) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.y, p = blockIdx.x, c = blockIdx.z * blockDim.x + threadIdx.x;
+  const int t0 = cu_seqlens[s] + p * MG_CH, t1 = min(cu_seqlens[s + 1], t0 + MG_CH);
+  if (c >= N || t0 >= t1) return;
+  const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    float keep, add;
+    mingru_gate(proj + (size_t)t * row, z_off, x_off, c, b_z, b_x, keep, add);
+    A *= keep;
+    B = fmaf(keep, B, add);
+  }
+  float* ab = AB + (((size_t)s * max_pieces + p) * 2) * N;
+  ab[c] = A;
+  ab[N + c] = B;
+}
+
+// the begin state of every piece (written over A) and the sequence's new state
+__global__ void __launch_bounds__(128) mingru_carry_kernel(float* __restrict__ AB, float* __restrict__ state,
+                                                           const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
+                                                           int N, int max_pieces) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  const int n = cu_seqlens[s + 1] - cu_seqlens[s];
+  const int pieces = (n + MG_CH - 1) / MG_CH;
+  float* sp = state + (size_t)seq_slots[s] * N + c;
+  float S = *sp;
+  for (int p = 0; p < pieces; ++p) {
+    float* ab = AB + (((size_t)s * max_pieces + p) * 2) * N;
+    const float A = ab[c], B = ab[N + c];
+    ab[c] = S;
+    S = fmaf(A, S, B);
+  }
+  *sp = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) mingru_apply_kernel(const T* __restrict__ proj, int row, int z_off, int x_off, int g_off,
+                                                           const float* __restrict__ bz, const float* __restrict__ bx,
+                                                           const float* __restrict__ AB, T* __restrict__ out,
+                                                           const int* __restrict__ cu_seqlens, int N, int max_pieces) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.y, p = blockIdx.x, c = blockIdx.z * blockDim.x + threadIdx.x;
+  const int t0 = cu_seqlens[s] + p * MG_CH, t1 = min(cu_seqlens[s + 1], t0 + MG_CH);
+  if (c >= N || t0 >= t1) return;
+  const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
+  float S = AB[(((size_t)s * max_pieces + p) * 2) * N + c];
+  for (int t = t0; t < t1; ++t) {
+    const T* r = proj + (size_t)t * row;
+    float keep, add;
+    mingru_gate(r, z_off, x_off, c, b_z, b_x, keep, add);
+    S = fmaf(keep, S, add);
+    out[(size_t)t * N + c] = from_f32<T>(S * silu_f32(to_f32(r[g_off + c])));
+  }
+}
+
+template <typename T>
+static int mingru_launch(const void* proj, int row, int z_off, int x_off, int g_off, const float* bz, const float* bx,
+                         float* state, void* out, float* scratch, const int* cu_seqlens, const int* seq_slots, int S, int N,
+                         int max_new, cudaStream_t stream) {
+  const int cb = (N + 127) / 128;
+  if (max_new <= 2 * MG_CH || scratch == nullptr)
+    return sx_launch(mingru_scan_kernel<T>, dim3(S, cb), dim3(128), 0, stream, (const T*)proj, row, z_off, x_off, g_off, bz, bx,
+                     state, (T*)out, cu_seqlens, seq_slots, N);
+  const int max_pieces = (max_new + MG_CH - 1) / MG_CH;
+  int e = sx_launch(mingru_piece_kernel<T>, dim3(max_pieces, S, cb), dim3(128), 0, stream, (const T*)proj, row, z_off, x_off, bz,
+                    bx, scratch, cu_seqlens, N, max_pieces);
+  if (e) return e;
+  e = sx_launch(mingru_carry_kernel, dim3(S, cb), dim3(128), 0, stream, scratch, state, cu_seqlens, seq_slots, N, max_pieces);
+  if (e) return e;
+  return sx_launch(mingru_apply_kernel<T>, dim3(max_pieces, S, cb), dim3(128), 0, stream, (const T*)proj, row, z_off, x_off, g_off,
+                   bz, bx, (const float*)scratch, (T*)out, cu_seqlens, N, max_pieces);
+}
+
+// scratch: float32 [S, ceil(max_new / 64), 2, N], or null (then the sequential kernel runs whatever the length)
+extern "C" int sx_mingru(const void* proj, int row, int z_off, int x_off, int g_off, const float* bz, const float* bx,
+                         float* state, void* out, float* scratch, const int* cu_seqlens, const int* seq_slots, int S, int N,
+                         int max_new, int dt, cudaStream_t stream) {
+  if (S <= 0 || N <= 0) return 0;
+  if (S > 65535) return SX_ERR_SIZE;
+  if (dt == SX_F32)
+    return mingru_launch<float>(proj, row, z_off, x_off, g_off, bz, bx, state, out, scratch, cu_seqlens, seq_slots, S, N, max_new, stream);
+  if (dt == SX_BF16)
+    return mingru_launch<bf16>(proj, row, z_off, x_off, g_off, bz, bx, state, out, scratch, cu_seqlens, seq_slots, S, N, max_new, stream);
+  return SX_ERR_DTYPE;
+}
+extern "C" int sx_mingru_piece_tokens() { return MG_CH; }
+
+// ---------------------------------------------------------------------------------------
+// Retention: linear attention with a fixed decay per head, no softmax and no denominator.  Per head, with
+// q, k of size D and v of size E (columns q_off + head*D, k_off + head*D, v_off + head*E of `proj` [T, row]):
+//   S <- decay S + (k * kscale) v^T   ([D, E], 32-bit, state [slots, heads, D, E]),   o = S^T q,
+//   out[t, head*E + e] = o[e] / sqrt(mean_e(o^2) + eps) * silu(gate[t, g_off + head*E + e]) * out_scale
+// (the gate and the unit norm are optional).  One block per (sequence, head) walks the sequence's tokens; S lies in
+// shared memory; thread (g, e) owns column e and the rows d = g, g + G, ... of S.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) retention_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
+                                                        int g_off, const float* __restrict__ decay, float kscale, float eps,
+                                                        int unit_norm, float out_scale, float* __restrict__ state,
+                                                        T* __restrict__ out, int out_stride, const int* __restrict__ cu_seqlens,
+                                                        const int* __restrict__ seq_slots, int heads, int D, int E) {
+  extern __shared__ float sm[];
+  float* S = sm;                     // D * E
+  float* qs = S + (size_t)D * E;     // D
+  float* ks = qs + D;                // D
+  float* vs = ks + D;                // E
+  float* part = vs + E;              // G * E
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.x, hd = blockIdx.y, tid = threadIdx.x;
+  const int G = blockDim.x / E;                      // E <= blockDim.x is checked by the host
+  const int e = tid % E, g = tid / E;
+  const bool live = g < G;
+  const float dc = decay[hd];
+  float* sp = state + ((size_t)seq_slots[s] * heads + hd) * D * E;
+  for (int i = tid; i < D * E; i += blockDim.x) S[i] = sp[i];
+  const int t0 = cu_seqlens[s], t1 = cu_seqlens[s + 1];
+  for (int t = t0; t < t1; ++t) {
+    const T* r = proj + (size_t)t * row;
+    __syncthreads();                                  // the token before is done with qs, ks, vs, part
+    for (int i = tid; i < D; i += blockDim.x) {
+      qs[i] = to_f32(r[q_off + hd * D + i]);
+      ks[i] = to_f32(r[k_off + hd * D + i]) * kscale;
+    }
+    for (int i = tid; i < E; i += blockDim.x) vs[i] = to_f32(r[v_off + hd * E + i]);
+    __syncthreads();
+    if (live) {
+      const float ve = vs[e];
+      float acc = 0.f;
+      for (int d = g; d < D; d += G) {
+        const float x = fmaf(dc, S[d * E + e], ks[d] * ve);
+        S[d * E + e] = x;
+        acc = fmaf(x, qs[d], acc);
+      }
+      part[g * E + e] = acc;
+    }
+    __syncthreads();
+    float o = 0.f;
+    if (tid < E)
+      for (int i = 0; i < G; ++i) o += part[i * E + tid];
+    float inv = 1.f;
+    if (unit_norm) inv = rsqrtf(block_sum(tid < E ? o * o : 0.f, red) / (float)E + eps);
+    if (tid < E) {
+      float x = o * inv;
+      if (g_off >= 0) x *= silu_f32(to_f32(r[g_off + hd * E + tid]));
+      out[(size_t)t * out_stride + hd * E + tid] = from_f32<T>(x * out_scale);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < D * E; i += blockDim.x) sp[i] = S[i];
+}
+
+extern "C" int sx_retention(const void* proj, int row, int q_off, int k_off, int v_off, int g_off, const float* decay,
+                            float kscale, float eps, int unit_norm, float out_scale, float* state, void* out, int out_stride,
+                            const int* cu_seqlens, const int* seq_slots, int S, int heads, int D, int E, int dt,
+                            cudaStream_t stream) {
+  if (S <= 0 || heads <= 0) return 0;
+  if (D <= 0 || E <= 0 || E > 256 || heads > 65535) return SX_ERR_SIZE;
+  const int G = 256 / E;
+  const size_t smem = ((size_t)D * E + 2 * D + E + (size_t)G * E) * sizeof(float);
+  if (smem > 200 * 1024) return SX_ERR_SIZE;
+  const dim3 grid(S, heads);
+#define RET_GO(TT)                                                                                                          \
+  {                                                                                                                         \
+    if (smem > 48 * 1024) {                                                                                                 \
+      cudaError_t e = cudaFuncSetAttribute(retention_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      if (e != cudaSuccess) return (int)e;                                                                                  \
+    }                                                                                                                       \
+    return sx_launch(retention_kernel<TT>, grid, dim3(256), smem, stream, (const TT*)proj, row, q_off, k_off, v_off, g_off, \
+                     decay, kscale, eps, unit_norm, out_scale, state, (TT*)out, out_stride, cu_seqlens, seq_slots, heads, D, E); \
+  }
+  if (dt == SX_F32) RET_GO(float)
+  if (dt == SX_BF16) RET_GO(bf16)
+#undef RET_GO
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// Capped gated activation of a stacked gate/up product gu [T, 2I]:
+//   g = min(gu[t, i], limit),  u = clamp(gu[t, I + i], -limit, limit),  out = g * sigmoid(alpha g) * (u + 1)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void capped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, float alpha, float limit, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / I;
+  const int i = (int)(idx - t * I);
+  const float g = fminf(to_f32(gu[t * 2 * I + i]), limit);
+  const float u = fminf(fmaxf(to_f32(gu[t * 2 * I + I + i]), -limit), limit);
+  out[idx] = from_f32<T>(g * sigmoid_f32(alpha * g) * (u + 1.f));
+}
+extern "C" int sx_capped_glu(const void* gu, void* out, int n_tokens, int I, float alpha, float limit, int dt, cudaStream_t stream) {
+  const size_t n = (size_t)n_tokens * I;
+  if (n == 0) return 0;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (dt == SX_F32) return sx_launch(capped_glu_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, (float*)out, I, alpha, limit, n);
+  if (dt == SX_BF16) return sx_launch(capped_glu_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, I, alpha, limit, n);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// h[t, c] += delta[t, c] + rows[t, c] + vec[c]   (each of the three optional; h, rows and vec 32-bit)
+// ---------------------------------------------------------------------------------------
+template <typename TD>
+__global__ void stream_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ rows,
+                                  const float* __restrict__ vec, int H, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  float v = h[idx];
+  if (delta) v += to_f32(delta[idx]);
+  if (rows) v += rows[idx];
+  if (vec) v += vec[idx % H];
+  h[idx] = v;
+}
+extern "C" int sx_stream_add(float* h, const void* delta, int delta_dt, const float* rows, const float* vec, int n_tokens, int H,
+                             cudaStream_t stream) {
+  const size_t n = (size_t)n_tokens * H;
+  if (n == 0) return 0;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (delta_dt == SX_F32) return sx_launch(stream_add_kernel<float>, grid, dim3(256), 0, stream, h, (const float*)delta, rows, vec, H, n);
+  if (delta_dt == SX_BF16) return sx_launch(stream_add_kernel<bf16>, grid, dim3(256), 0, stream, h, (const bf16*)delta, rows, vec, H, n);
+  return SX_ERR_DTYPE;
+}

@@ -7,9 +7,10 @@ from ..config.registry import load_config, resolve_architecture
 from ..parts.base import Runtime
 from ..weights.loader import SafetensorsSource, WeightSource
 from . import qwen3 as _qwen3  # registers the architecture
-from .decoder import DecoderModel, LayerRun
+from . import vemedra as _vemedra  # registers the architecture
+from .decoder import DecoderModel, Inject, LayerRun, StreamVectors
 
-__all__ = ["DecoderModel", "LayerRun", "model_skeleton", "load_model", "parse_dtype"]
+__all__ = ["DecoderModel", "Inject", "LayerRun", "StreamVectors", "model_skeleton", "load_model", "parse_dtype"]
 
 
 def parse_dtype(name) -> torch.dtype:

@@ -4,7 +4,11 @@
 names a layer and the cache entry it works on, so a schedule may run a layer
 twice (two runs, each with a cache entry of its own) or let a layer read the
 cache another layer wrote (``write_cache=False`` and that layer's entry).  The
-default schedule runs every layer once on its own entry.
+default schedule runs every layer once on its own entry.  Between two runs a
+schedule may hold an ``Inject``: vectors added into the residual stream there
+(the embedding output once more, a row of the model's table of stream vectors),
+which is what a model needs that runs a stretch of layers several times and
+marks each pass.
 
 Step (crates/synaptix-models/llm/common/src/model.rs:1057-1117,1160-1262):
 embedding -> runs -> final norm on the rows whose logits are wanted -> output
@@ -19,7 +23,8 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..cache.store import CacheRequest
-from ..parts.base import Norm, Part, PendingLinear, Runtime, StepContext
+from .. import ops
+from ..parts.base import Norm, Part, PendingLinear, Runtime, StepContext, plain, to_device_f32
 from ..parts.embedding import Embedding, OutputHead
 from ..weights.loader import TensorSpec, WeightSource, bind_tensors
 
@@ -31,17 +36,46 @@ class LayerRun:
     write_cache: bool = True
 
 
+@dataclasses.dataclass(frozen=True)
+class Inject:
+    """Between two runs: ``h += embedding output`` (the stream as the embedding left it) if ``embedding``, and
+    ``h += stream_vectors[row]`` if ``row`` is not ``None``."""
+    embedding: bool = False
+    row: Optional[int] = None
+
+
+class StreamVectors(Part):
+    """A table ``[rows, width]`` of vectors that a schedule adds into the residual stream (``Inject.row``)."""
+
+    def __init__(self, name: str, rows: int, width: int):
+        self.name, self.rows, self.width = name, rows, width
+        self.table: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.rows, self.width), "embedding")}
+
+    def bind(self, tensors, rt: Runtime) -> None:
+        self.table = to_device_f32(tensors[self.name], rt)
+
+
 class DecoderModel(Part):
     def __init__(self, config, embedding: Embedding, layers: Sequence[Part], final_norm: Norm,
-                 head: OutputHead, schedule: Optional[Sequence[LayerRun]] = None,
-                 stop_token_ids: Sequence[int] = ()):
+                 head: OutputHead, schedule: Optional[Sequence] = None,
+                 stop_token_ids: Sequence[int] = (), stream_vectors: Optional[StreamVectors] = None):
         self.config = config
         self.embedding = embedding
         self.layers = list(layers)
         self.final_norm = final_norm
         self.head = head
-        self.schedule = list(schedule) if schedule is not None else [
+        self.steps = list(schedule) if schedule is not None else [
             LayerRun(i, i) for i in range(len(self.layers))]
+        self.schedule = [r for r in self.steps if isinstance(r, LayerRun)]
+        self.stream_vectors = stream_vectors
+        for r in self.steps:
+            if isinstance(r, Inject) and r.row is not None and (
+                    stream_vectors is None or not (0 <= r.row < stream_vectors.rows)):
+                raise ValueError(f"the schedule adds stream vector {r.row}, which the model does not have")
+        self._keeps_embedding = any(isinstance(r, Inject) and r.embedding for r in self.steps)
         self.stop_token_ids = tuple(stop_token_ids)
         self.runtime: Optional[Runtime] = None
         n_entries = 1 + max((r.cache_entry for r in self.schedule), default=-1)
@@ -63,7 +97,8 @@ class DecoderModel(Part):
         return self.head.vocab
 
     def children(self) -> List[Part]:
-        return [self.embedding] + self.layers + [self.final_norm, self.head]
+        extra = [self.stream_vectors] if self.stream_vectors is not None else []
+        return [self.embedding] + extra + self.layers + [self.final_norm, self.head]
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
@@ -83,11 +118,22 @@ class DecoderModel(Part):
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         """Logits float32 ``[n_want, vocab]`` for ``ctx.want_rows``."""
         h = self.embedding.forward(ctx.token_ids)
+        h0 = self.embedding.forward(ctx.token_ids) if self._keeps_embedding else None     # h is summed into in place
         pending = None
-        for run in self.schedule:
+        observe = getattr(ctx, "observe", None)
+        n_run = 0
+        for run in self.steps:
+            if isinstance(run, Inject):
+                ops.stream_add(h, plain(pending), h0 if run.embedding else None,
+                               self.stream_vectors.table[run.row] if run.row is not None else None)
+                pending = None
+                continue
             if isinstance(pending, PendingLinear) and not getattr(self.layers[run.layer], "takes_pending_product", False):
                 pending = pending.materialize()
             h, pending = self.layers[run.layer].forward(h, pending, ctx, cache.view(run.cache_entry), run.write_cache)
+            if observe is not None:              # the stream after this run: h with the branch not yet added
+                observe(n_run, h, plain(pending))
+            n_run += 1
         if isinstance(pending, PendingLinear) and not self.final_norm.takes_pending_product:
             pending = pending.materialize()
         if getattr(ctx, "want_all", False):        # every row, in order: no gather, and the norm may fuse

@@ -21,11 +21,13 @@ from .gemm_ws import gemm_ws, gemm_ws_residual, ws_supported
 from .options import OPTIONS, KernelOptions, options, set_options
 from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, embed_gather, gemm_generic, qkv_prepare,
                       residual_add, rope_table, silu_mul)
+from .sequence import add_rmsnorm_conv, capped_glu, mingru, retention, stream_add
 
 __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "decode_begin", "check_status", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
-           "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table"]
+           "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table",
+           "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add"]
 
 
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
@@ -262,9 +264,17 @@ def attention_from_projection(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages:
 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor,
-              nh: int, nkv: int, hd: int, scale: float, window: Optional[int]) -> torch.Tensor:
+              nh: int, nkv: int, hd: int, scale: float, window: Optional[int], *, vd: Optional[int] = None,
+              softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+              out: Optional[torch.Tensor] = None, out_col: int = 0, out_scale: float = 1.0) -> torch.Tensor:
     """Causal attention of the step's packed queries over the cache (which already holds
-    this step's keys and values)."""
+    this step's keys and values).  The options are those of ``attn_generic``: value heads of
+    another size, capped scores, a sink per head, chunks of positions, a wider output."""
+    plain = (vd in (None, hd) and softcap is None and sinks is None and chunk is None and out is None
+             and out_scale == 1.0)
+    if not plain:
+        return attn_generic(q, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, nh, nkv, hd, scale, window,
+                            out, vd=vd, softcap=softcap, sinks=sinks, chunk=chunk, out_scale=out_scale, out_col=out_col)
     if fast_supported(q.dtype, nh, nkv, hd):
         if ctx.all_single:
             max_pages = (ctx.max_len + 63) // 64

@@ -81,32 +81,43 @@ def qkv_prepare(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.
                 v_pages: Optional[torch.Tensor], wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
                 inv_freq: Optional[torch.Tensor], rotary_dim: int, eps: float, positions: torch.Tensor,
                 seq_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, hd: int,
-                pages_like: Optional[torch.Tensor] = None) -> None:
+                pages_like: Optional[torch.Tensor] = None, vd: Optional[int] = None, col: int = 0) -> None:
     """Per-head RMSNorm (optional), rotate-half rotation (optional) and the cache write.
 
     ``qkv`` ``[T, (nh + 2 nkv) * hd]``; q heads go to ``q_out`` ``[T, nh * hd]``; k and v
     heads go into the pages ``[n_pages, nkv, 64, hd]`` of the token's sequence at the
     token's position.  With ``k_pages``/``v_pages`` ``None`` nothing is written to the cache
-    (a layer that reads another layer's cache).
+    (a layer that reads another layer's cache).  With ``vd`` the value heads have ``vd``
+    elements (pages ``[n_pages, nkv, 64, vd]``), and ``qkv`` may be wider than the heads need:
+    the q, k and v heads begin at column ``col`` of a row and other columns may lie around them.
     """
     require_cuda(qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, positions, seq_of_token, block_table)
     T = qkv.shape[0]
-    if qkv.shape[1] != (nh + 2 * nkv) * hd:
+    strided = vd is not None
+    vd = hd if vd is None else vd
+    if (qkv.shape[1] < col + (nh + nkv) * hd + nkv * vd) if strided else (qkv.shape[1] != (nh + 2 * nkv) * hd or col):
         raise KernelError("qkv_prepare: qkv has the wrong width")
     if qkv.dtype != q_out.dtype:
         raise KernelError("qkv_prepare: qkv and q must share a dtype")
     n_pages = 0
-    for pg in (k_pages, v_pages):
+    for pg, d in ((k_pages, hd), (v_pages, vd)):
         if pg is None:
             continue
         if pg.dtype != qkv.dtype:
             raise KernelError("qkv_prepare: qkv and the cache must share a dtype")
-        if pg.dim() != 4 or tuple(pg.shape[1:]) != (nkv, 64, hd):
-            raise KernelError("qkv_prepare: cache pages must be [n_pages, nkv, 64, hd]")
+        if pg.dim() != 4 or tuple(pg.shape[1:]) != (nkv, 64, d):
+            raise KernelError("qkv_prepare: cache pages must be [n_pages, nkv, 64, head size]")
         n_pages = pg.shape[0]
     for t in (positions, seq_of_token, block_table):
         if t.dtype != torch.int32:
             raise KernelError("qkv_prepare: index tensors are int32")
+    if strided:
+        check(fn("generic", "sx_qkv_prepare_strided")(
+            ptr(qkv if col == 0 else qkv.view(-1)[col:]), ptr(q_out), ptr(k_pages), ptr(v_pages), ptr(wq), ptr(wk), ptr(inv_freq), c_int(rotary_dim),
+            c_float(eps), ptr(positions), ptr(seq_of_token), ptr(block_table), c_int(block_table.shape[1]),
+            c_int(T), c_int(nh), c_int(nkv), c_int(hd), c_int(n_pages), c_int(dt_code(qkv.dtype)),
+            c_int(qkv.shape[1]), c_int(vd), stream()), "qkv_prepare")
+        return
     check(fn("generic", "sx_qkv_prepare")(
         ptr(qkv), ptr(q_out), ptr(k_pages), ptr(v_pages), ptr(wq), ptr(wk), ptr(inv_freq), c_int(rotary_dim),
         c_float(eps), ptr(positions), ptr(seq_of_token), ptr(block_table), c_int(block_table.shape[1]),
@@ -127,16 +138,31 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor):
 
 def attn_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
                  seq_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, hd: int,
-                 scale: float, window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal (optionally windowed) attention of packed tokens over the paged cache, 32-bit math."""
-    require_cuda(q, k_pages, v_pages, positions, seq_of_token, block_table, out)
+                 scale: float, window: Optional[int] = None, out: Optional[torch.Tensor] = None, *,
+                 vd: Optional[int] = None, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
+                 chunk: Optional[int] = None, out_scale: float = 1.0, out_col: int = 0) -> torch.Tensor:
+    """Causal (optionally windowed) attention of packed tokens over the paged cache, 32-bit math.
+
+    Options: ``vd`` value head size (default ``hd``); ``softcap``: scores become ``softcap * tanh(score / softcap)``;
+    ``sinks`` float32 ``[nh]``: ``exp(sink)`` joins each head's softmax denominator; ``chunk``: a query sees only
+    keys of its own chunk of that many positions; ``out`` may be wider than ``nh * vd`` (the result fills its columns
+    from ``out_col`` on) and is multiplied by ``out_scale``."""
+    require_cuda(q, k_pages, v_pages, positions, seq_of_token, block_table, out, sinks)
     T = q.shape[0]
+    vd = hd if vd is None else vd
     if out is None:
-        out = torch.empty((T, nh * hd), dtype=q.dtype, device=q.device)
-    check(fn("generic", "sx_attn_generic")(
-        ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(positions), ptr(seq_of_token), ptr(block_table),
+        out = torch.empty((T, nh * vd), dtype=q.dtype, device=q.device)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh):
+        raise KernelError("attn_generic: sinks are float32, one per query head")
+    if out.dtype != q.dtype or out_col + nh * vd > out.shape[1]:
+        raise KernelError("attn_generic: the output does not fit")
+    o = out if out_col == 0 else out.view(-1)[out_col:]
+    check(fn("generic", "sx_attn_generic_ex")(
+        ptr(q), ptr(k_pages), ptr(v_pages), ptr(o), ptr(positions), ptr(seq_of_token), ptr(block_table),
         c_int(block_table.shape[1]), c_int(T), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
-        c_int(0 if window is None else int(window)), c_int(dt_code(q.dtype)), stream()), "attn_generic")
+        c_int(0 if window is None else int(window)), c_int(dt_code(q.dtype)), c_int(vd),
+        c_float(0.0 if softcap is None else float(softcap)), ptr(sinks), c_int(0 if chunk is None else int(chunk)),
+        c_int(out.shape[1]), c_float(out_scale), stream()), "attn_generic")
     return out
 
 

@@ -1,13 +1,16 @@
 from .attention import Attention
 from .base import (FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, PositionEncoding, Runtime, ScaledRows,
                    StepContext)
-from .block import PreNormBlock
+from .block import ConvPreNormBlock, PreNormBlock, TokenConv
 from .embedding import Embedding, OutputHead
-from .linear import Linear
-from .mlp import SwiGLU
+from .linear import JoinedLinear, Linear
+from .mlp import CappedGLU, SwiGLU
 from .norm import RMSNorm
+from .parallel import ParallelMixers
+from .recurrent import MinGRU, Retention
 from .rope import NoPosition, RotaryHalf, rotary_inv_freq
 
 __all__ = ["Attention", "FeedForward", "Mixer", "Norm", "Part", "PendingLinear", "PendingNorm", "ScaledRows", "PositionEncoding", "Runtime",
-           "StepContext", "PreNormBlock", "Embedding", "OutputHead", "Linear", "SwiGLU", "RMSNorm",
-           "NoPosition", "RotaryHalf", "rotary_inv_freq"]
+           "StepContext", "PreNormBlock", "ConvPreNormBlock", "TokenConv", "Embedding", "OutputHead", "Linear", "JoinedLinear",
+           "SwiGLU", "CappedGLU", "RMSNorm", "ParallelMixers", "MinGRU", "Retention", "NoPosition", "RotaryHalf",
+           "rotary_inv_freq"]

@@ -62,12 +62,13 @@ class StepContext:
     """
     __slots__ = ("token_ids", "positions", "seq_of_token", "cu_seqlens", "seq_past", "seq_lens",
                  "seq_slots", "block_tables", "want_rows", "n_tokens", "n_seqs", "n_want",
-                 "max_new", "max_len", "all_single", "runtime", "scratch", "host", "want_all")
+                 "max_new", "max_len", "all_single", "runtime", "scratch", "host", "want_all", "observe")
 
     def __init__(self, **kw):
         self.scratch = {}
         self.host = None
         self.want_all = False      # want_rows is 0..n_tokens-1 in order
+        self.observe = None        # callable(run number, h, pending): called after every layer run (debugging, tests)
         for k, v in kw.items():
             setattr(self, k, v)
 

@@ -4,14 +4,24 @@
 ``h += mixer(norm1(h)); h += ffn(norm2(h))``.  The residual stream ``h`` is
 float32; each branch output is handed on as ``pending`` and added by the next
 norm's kernel, so a sum and a norm are one pass over memory.
+
+``ConvPreNormBlock``: the same arrangement with a short causal convolution over time
+between each norm and its sublayer: what a sublayer reads is ``y + conv(y)`` with
+``y = norm(h)``, ``conv(y)_t = sum_j w[:, j] * y_(t - taps + 1 + j)`` per channel, zeros
+before the sequence's start (``TokenConv``).  The last ``taps - 1`` inputs of each
+convolution are part of a sequence's state; the feed-forward half may be absent.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, ScaledRows, StepContext
+from .. import ops
+from ..cache.store import BundleRequest, StateRequest
+from ..weights.loader import TensorSpec
+from .base import (FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, StepContext, plain,
+                   to_device_f32)
 
 
 class PreNormBlock(Part):
@@ -44,3 +54,55 @@ class PreNormBlock(Part):
         if isinstance(y, (PendingNorm, ScaledRows)):
             h = y.h_after()
         return h, m
+
+
+class TokenConv(Part):
+    """The taps of a short causal convolution over time, one filter per channel: tensor ``[width, taps]``, no bias."""
+
+    def __init__(self, weight_name: str, width: int, taps: int):
+        if taps < 1:
+            raise ValueError("a convolution has at least one tap")
+        self.weight_name, self.width, self.taps = weight_name, width, taps
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.weight_name: TensorSpec((self.width, self.taps), "bias")}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.weight = to_device_f32(tensors[self.weight_name], rt)
+
+    def state_request(self) -> StateRequest:
+        """The last ``taps - 1`` inputs of a sequence, oldest first, in 32-bit."""
+        return StateRequest((self.taps - 1, self.width), torch.float32)
+
+
+class ConvPreNormBlock(Part):
+    """``h += mixer(c1(norm1(h))); h += ffn(c2(norm2(h)))`` with ``c(y) = y + conv(y)``; ``norm2, conv2, ffn`` may all
+    be ``None`` (a layer without a feed-forward).  The norms are RMS norms with a plain gain (the fused kernel computes
+    them).  Cache entry: the bundle (mixer's request, conv1's inputs[, conv2's inputs])."""
+    takes_pending_product = False
+
+    def __init__(self, norm1: Norm, conv1: TokenConv, mixer: Mixer, norm2: Optional[Norm] = None,
+                 conv2: Optional[TokenConv] = None, ffn: Optional[FeedForward] = None):
+        if (norm2 is None) != (ffn is None) or (conv2 is None) != (ffn is None):
+            raise ValueError("norm2, conv2 and ffn come together or not at all")
+        self.norm1, self.conv1, self.mixer = norm1, conv1, mixer
+        self.norm2, self.conv2, self.ffn = norm2, conv2, ffn
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm1, self.conv1, self.mixer, self.norm2, self.conv2, self.ffn) if p is not None]
+
+    def cache_request(self):
+        items = [self.mixer.cache_request(), self.conv1.state_request()]
+        if self.ffn is not None:
+            items.append(self.conv2.state_request())
+        return BundleRequest(tuple(items))
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, views, write_cache: bool = True):
+        dtype = ctx.runtime.dtype
+        x = ops.add_rmsnorm_conv(h, plain(pending), self.norm1.weight, self.norm1.eps, self.conv1.weight, views[1], ctx, dtype)
+        a = self.mixer.forward(x, ctx, views[0], write_cache)
+        if self.ffn is None:
+            return h, a
+        y = ops.add_rmsnorm_conv(h, plain(a), self.norm2.weight, self.norm2.eps, self.conv2.weight, views[2], ctx, dtype)
+        return h, self.ffn.forward(y, ctx)

@@ -4,7 +4,9 @@ without bias, crates/synaptix-models/llm/common/src/weights.rs:49-51).
 
 ``Linear`` may bind several named matrices and stack them along the output
 dimension, so that q/k/v (or gate/up) become one product; the checkpoint keeps
-its separate tensors and names.
+its separate tensors and names.  ``JoinedLinear`` stacks along the INPUT
+dimension instead: the sum of several products ``sum_i x_i W_i^T`` as one
+product over the concatenated inputs.
 """
 from __future__ import annotations
 
@@ -62,3 +64,23 @@ class Linear(Part):
                 return y
             x = x.materialize()
         return ops.linear(x, self.weight, out_dtype=out_dtype, epilogue=epilogue)
+
+
+class JoinedLinear(Linear):
+    """``[x_1 | x_2 | ...] @ [W_1 | W_2 | ...].T = sum_i x_i W_i^T``: named matrices ``[out, in_i]`` stacked along their
+    inputs, so that branches that are added after their output projections share one product."""
+
+    def __init__(self, weight_names: Sequence[str], in_features: Sequence[int], out_features: int):
+        self.weight_names = list(weight_names)
+        self.in_parts = list(in_features)
+        self.in_features = sum(self.in_parts)
+        self.out_features = [out_features]
+        self.kind = "matrix"
+        self.weight = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {n: TensorSpec((self.out_features[0], i), self.kind) for n, i in zip(self.weight_names, self.in_parts)}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        ws = [to_device_matrix(tensors[n], rt) for n in self.weight_names]
+        self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=1).contiguous()

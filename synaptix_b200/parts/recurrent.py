@@ -1,0 +1,125 @@
+"""Mixers that carry a state of fixed size from token to token instead of keys and values.
+
+``MinGRU``: a gated recurrence per channel whose gates read only the current token.  With ``a_z, a_x, a_g`` the three
+projections of the input (``n`` channels each; the first two with a bias):
+
+    z = sigmoid(a_z),   cand = a_x + 1/2  if a_x >= 0  else sigmoid(a_x),
+    S_t = (1 - z) S_(t-1) + z cand,       out = Wo (S_t * silu(a_g))
+
+``Retention``: linear attention with a fixed decay per head, no softmax and no denominator.  Per head, with q and k of
+``dim`` and v of ``vdim`` elements:
+
+    S_t = decay S_(t-1) + (k_t k_scale) v_t^T,   o_t = S_t^T q_t,
+    out = Wo (o_t / rms(o_t) * silu(a_g))        (unit norm and gate optional)
+
+Both states start at zero, live in 32-bit in the cache's per-sequence state storage and go on from step to step; the
+gates, decays, norms and sums are 32-bit whatever the compute dtype.  Both parts can run alone (they own their
+projections) or ``shared``: beside other mixers under one owner that stacks the projections of all of them
+(``input_parts``, ``output_part``, ``mix``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.store import StateRequest
+from ..weights.loader import TensorSpec
+from .base import Mixer, Part, Runtime, StepContext, to_device_f32
+from .linear import Linear
+
+
+class MinGRU(Mixer):
+    accepts_lazy_input = False
+    can_defer_output = True
+
+    NAMES = {"z": "z", "x": "x", "g": "g", "o": "o", "z_bias": "z.b", "x_bias": "x.b"}
+
+    def __init__(self, prefix: str, width: int, channels: int, *, names: Optional[Mapping[str, str]] = None):
+        self.prefix, self.width, self.n = prefix, width, channels
+        self.names = dict(self.NAMES, **(names or {}))
+        p, n = prefix, self.names
+        self.zxg = Linear([p + n["z"], p + n["x"], p + n["g"]], width, [channels] * 3)
+        self.o = Linear(p + n["o"], channels, width)
+        self.bias_z: Optional[torch.Tensor] = None
+        self.bias_x: Optional[torch.Tensor] = None
+
+    def children(self) -> List[Part]:
+        return [self.zxg, self.o]
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.prefix + self.names["z_bias"]: TensorSpec((self.n,), "bias"),
+                self.prefix + self.names["x_bias"]: TensorSpec((self.n,), "bias")}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.bias_z = to_device_f32(tensors[self.prefix + self.names["z_bias"]], rt)
+        self.bias_x = to_device_f32(tensors[self.prefix + self.names["x_bias"]], rt)
+
+    def cache_request(self):
+        return StateRequest((self.n,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, state: torch.Tensor, write_cache: bool = True,
+                defer_output: bool = False):
+        a = self.zxg.forward(x)
+        y = ops.mingru(a, 0, self.n, 2 * self.n, self.n, self.bias_z, self.bias_x, state, ctx)
+        return self.o.deferred(y) if defer_output else self.o.forward(y)
+
+
+class Retention(Mixer):
+    accepts_lazy_input = False
+    can_defer_output = True
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+
+    def __init__(self, prefix: str, width: int, heads: int, dim: int, vdim: int, decay: Sequence[float], *,
+                 k_scale: Optional[float] = None, unit_norm_eps: Optional[float] = None, gated: bool = True,
+                 names: Optional[Mapping[str, str]] = None, shared: bool = False):
+        if len(decay) != heads:
+            raise ValueError(f"{len(decay)} decays for {heads} heads")
+        self.prefix, self.width = prefix, width
+        self.heads, self.dim, self.vdim = heads, dim, vdim
+        self.decay_values = [float(d) for d in decay]
+        self.k_scale = float(k_scale) if k_scale is not None else float(dim) ** -0.5
+        self.unit_norm_eps = unit_norm_eps
+        self.gated = bool(gated)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.shared = bool(shared)
+        self.proj = self.o = None
+        if not shared:
+            names_in, outs = zip(*self.input_parts())
+            self.proj = Linear(list(names_in), width, list(outs))
+            self.o = Linear(self.output_part()[0], self.output_part()[1], width)
+        self.decay: Optional[torch.Tensor] = None
+
+    def input_parts(self):
+        p, n = self.prefix, self.names
+        parts = [(p + n["q"], self.heads * self.dim), (p + n["k"], self.heads * self.dim), (p + n["v"], self.heads * self.vdim)]
+        if self.gated:
+            parts.append((p + n["g"], self.heads * self.vdim))
+        return parts
+
+    def output_part(self):
+        return self.prefix + self.names["o"], self.heads * self.vdim
+
+    def children(self) -> List[Part]:
+        return [] if self.shared else [self.proj, self.o]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32).to(rt.device)
+
+    def cache_request(self):
+        return StateRequest((self.heads, self.dim, self.vdim), torch.float32)
+
+    def mix(self, proj: torch.Tensor, col: int, ctx: StepContext, state: torch.Tensor, write_cache: bool = True,
+            out: Optional[torch.Tensor] = None, out_col: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+        hq, hv = self.heads * self.dim, self.heads * self.vdim
+        return ops.retention(proj, col, col + hq, col + 2 * hq, col + 2 * hq + hv if self.gated else None,
+                             self.heads, self.dim, self.vdim, self.decay, self.k_scale,
+                             self.unit_norm_eps if self.unit_norm_eps is not None else 0.0,
+                             self.unit_norm_eps is not None, state, ctx, out=out, out_col=out_col, out_scale=out_scale)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, state: torch.Tensor, write_cache: bool = True,
+                defer_output: bool = False):
+        y = self.mix(self.proj.forward(x), 0, ctx, state, write_cache)
+        return self.o.deferred(y) if defer_output else self.o.forward(y)

@@ -39,13 +39,14 @@ class RandomSource(WeightSource):
     """Seeded normal weights for a set of tensor specs.
 
     ``matrix`` ~ N(0, std_matrix), ``embedding`` ~ N(0, std_embedding),
-    ``gain`` ~ 1 + N(0, std_gain), ``table`` = zeros (int32).  Floating tensors
+    ``gain`` ~ 1 + N(0, std_gain), ``bias`` ~ N(0, std_bias) (biases, taps of short convolutions, sinks),
+    ``table`` = zeros (int32).  Floating tensors
     are drawn in float32 and stored as ``dtype`` (``gain_dtype`` for gains).
     """
 
     def __init__(self, specs: Mapping[str, TensorSpec], seed: int, *,
                  std_matrix: float = 0.02, std_embedding: Optional[float] = None,
-                 std_gain: float = 0.05, dtype: torch.dtype = torch.bfloat16,
+                 std_gain: float = 0.05, std_bias: float = 0.2, dtype: torch.dtype = torch.bfloat16,
                  gain_dtype: Optional[torch.dtype] = None, device: str = "cpu",
                  skip_optional: bool = True):
         self.specs = {n: s for n, s in specs.items() if not (s.optional and skip_optional)}
@@ -53,6 +54,7 @@ class RandomSource(WeightSource):
         self.std_matrix = float(std_matrix)
         self.std_embedding = float(std_matrix if std_embedding is None else std_embedding)
         self.std_gain = float(std_gain)
+        self.std_bias = float(std_bias)
         self.dtype = dtype
         self.gain_dtype = dtype if gain_dtype is None else gain_dtype
         self.device = torch.device(device)
@@ -69,6 +71,8 @@ class RandomSource(WeightSource):
         x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=self.device)
         if spec.kind == "gain":
             return (1.0 + self.std_gain * x).to(self.gain_dtype)
+        if spec.kind == "bias":
+            return (self.std_bias * x).to(self.dtype)
         if spec.kind == "embedding":
             return (self.std_embedding * x).to(self.dtype)
         if spec.kind == "matrix":
