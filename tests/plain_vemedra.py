@@ -5,7 +5,6 @@ folders with the ``safetensors`` package) and is what the GPU tests compare the 
 Notation: ``x`` is the residual stream ``[T, width]``, ``h`` what a sublayer reads, positions count from 0.
 """
 import json
-import math
 import os
 
 import torch
@@ -39,10 +38,6 @@ def token_conv(h, w):
     return out
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def mingru(h, W, p):
     """S_t = (1 - z_t) S_(t-1) + z_t c_t with z = sigmoid(Wz h + bz), c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0),
     u = Wx h + bx; out = Wo (S_t * silu(Wg h))."""
@@ -68,6 +63,33 @@ def rotate_half(x, pos, dims, base):
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
 
 
+def chunk_sink_heads(q, k, v, pos, sinks, scale, cap, size):
+    """q [T, H, D], k [T, G, D], v [T, G, Dv] of ONE sequence at positions ``pos``: softmax attention in which position i
+    sees j <= i of its own chunk of ``size`` positions (None: all), scores capped by ``cap * tanh(. / cap)`` (None: not),
+    and exp(sink_h) in the denominator (None: no sink).  Returns [T, H, Dv]."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    see = pos[None, :] <= pos[:, None]
+    if size is not None:
+        see = see & ((pos[None, :] // size) == (pos[:, None] // size))
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for hh in range(H):
+        g = hh // (H // G)
+        s = (q[:, hh] @ k[:, g].T) * scale
+        if cap is not None:
+            s = cap * torch.tanh(s / cap)
+        s = s.masked_fill(~see, float("-inf"))
+        top = s.max(dim=-1).values
+        if sinks is not None:
+            top = torch.maximum(top, sinks[hh])
+        e = torch.exp(s - top[:, None])
+        den = e.sum(dim=-1)
+        if sinks is not None:
+            den = den + torch.exp(sinks[hh] - top)
+        out[:, hh] = (e / den[:, None]) @ v[:, g]
+    return out
+
+
 def chunk_sink_attention(h, W, p, m):
     """Grouped-query softmax attention inside chunks of ``mask.size`` positions, with capped scores and a sink."""
     T = h.shape[0]
@@ -76,21 +98,10 @@ def chunk_sink_attention(h, W, p, m):
     k = (h @ W[p + "k"].T).view(T, G, D)
     v = (h @ W[p + "v"].T).view(T, G, Dv)
     pos = torch.arange(T)
-    q = rotate_half(q, pos, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_half(k, pos, m["rot"]["dims"], m["rot"]["base"])
-    size, cap = m["mask"]["size"], m["softcap"]
-    see = (pos[None, :] <= pos[:, None]) & ((pos[None, :] // size) == (pos[:, None] // size))
-    out = torch.zeros(T, H, Dv, dtype=h.dtype)
-    for hh in range(H):
-        g = hh // (H // G)
-        s = (q[:, hh] @ k[:, g].T) * m["scale"]
-        s = cap * torch.tanh(s / cap)
-        s = s.masked_fill(~see, float("-inf"))
-        sink = W[p + "sink"][hh]
-        top = torch.maximum(s.max(dim=-1).values, sink)
-        e = torch.exp(s - top[:, None])
-        den = e.sum(dim=-1) + torch.exp(sink - top)
-        out[:, hh] = (e / den[:, None]) @ v[:, g]
+    if m.get("rot"):
+        q = rotate_half(q, pos, m["rot"]["dims"], m["rot"]["base"])
+        k = rotate_half(k, pos, m["rot"]["dims"], m["rot"]["base"])
+    out = chunk_sink_heads(q, k, v, pos, W[p + "sink"], m["scale"], m.get("softcap"), (m.get("mask") or {}).get("size"))
     return out.reshape(T, H * Dv) @ W[p + "o"].T
 
 
