@@ -39,12 +39,12 @@ struct AtPrep {
   int n_pages;
 };
 
-template <int HD, bool PREP>
+template <int HD, bool PREP, bool EX = false>
 __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int maxp, int nh, int nkv,
-    float scale_log2, int window, int n_splits, int* __restrict__ counters, const AtPrep prep) {
+    float scale_log2, int window, int n_splits, int* __restrict__ counters, const AtPrep prep, const AtExtra ex) {
   using L = AtLayout<HD>;
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ __align__(16) bf16 q_s[PREP ? 16 * HD : 8];       // the group's prepared query heads
@@ -55,7 +55,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int len = seq_lens[seq];
   const int pos = len - 1;                                   // the query's position
-  const int lo = window > 0 ? max(0, len - window) : 0;      // first visible key
+  int lo = window > 0 ? max(0, len - window) : 0;            // first visible key
+  if (EX && ex.chunk > 0) lo = max(lo, (pos / ex.chunk) * ex.chunk);
   const int p_first = lo >> 6, p_end = (len + 63) >> 6;
   const int total = p_end - p_first;
   const int per = (total + n_splits - 1) / n_splits;
@@ -161,6 +162,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     }
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // the scale that turns the running maxima into the log2 domain (1 when the scores are capped: they are there already)
+  const float sl_m = (EX && ex.cap_log2 > 0.f) ? 1.f : scale_log2;
+  if (EX && ex.sinks && warp == 0 && split == 0) {            // the sink counts once: in the first warp of the first split
+    if (g < G) { m[0] = ex.sinks[kvh * G + g] * 1.4426950408889634f / sl_m; l[0] = t == 0 ? 1.f : 0.f; }
+    if (g + 8 < G) { m[1] = ex.sinks[kvh * G + g + 8] * 1.4426950408889634f / sl_m; l[1] = t == 0 ? 1.f : 0.f; }
+  }
   float o[HD / 8][4];
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -183,7 +190,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     const unsigned char* st = smem + (i % AT_STAGES_DECODE) * L::STAGE;
     // this warp's 16 keys of the page; all fragment rows sit at the same position
     const int jb = (p0 + i) * 64;
-    if (jb + 63 > pos || (window > 0 && jb <= pos - window))
+    if (EX)
+      attend_tile<HD, 2, true, true>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o, lo, lo,
+                                     ex.cap_log2, ex.cap_in);
+    else if (jb + 63 > pos || (window > 0 && jb <= pos - window))
       attend_tile<HD, 2, true>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o);
     else      // the whole page is visible: no comparisons
       attend_tile<HD, 2, false>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o);
@@ -192,8 +202,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   __syncthreads();
 
   // the running maxima are of raw scores; the merges below work in the scaled (log2) domain
-  m[0] *= scale_log2;
-  m[1] *= scale_log2;
+  m[0] *= sl_m;
+  m[1] *= sl_m;
   // rows' sums over the 4 lanes that share a row
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -232,7 +242,9 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
       O += wo[(w * 16 + r) * HD + d] * f;
     }
     const int head = kvh * G + r;
-    if (n_splits == 1) {
+    if (EX) {                                                // one split; the output's rows may be wider than the heads
+      out[(size_t)seq * ex.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum * ex.out_scale : 0.f);
+    } else if (n_splits == 1) {
       out[((size_t)seq * nh + head) * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
     } else {
       const size_t pi = ((size_t)seq * nh + head) * n_splits + split;
@@ -240,7 +252,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
       if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = Lsum; }
     }
   }
-  if (n_splits == 1 || counters == nullptr) return;      // without counters a second kernel merges
+  if (EX || n_splits == 1 || counters == nullptr) return;      // without counters a second kernel merges
 
   // The block that finishes last for this (sequence, kv head) merges all splits, in split order.
   // counters[seq * nkv + kvh] counts finished blocks and is set back to zero by the last one, so
@@ -300,12 +312,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
 // =======================================================================================
 // prefill: grid (n_tiles, nh); tile i covers query rows tile_q0[i] .. +63 of sequence tile_seq[i]
 // =======================================================================================
-template <int HD>
+template <int HD, bool EX = false>
 __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
     const int* __restrict__ cu_seqlens, const int* __restrict__ seq_past, const int* __restrict__ seq_lens,
-    const int* __restrict__ block_table, int maxp, int nh, int nkv, float scale_log2, int window) {
+    const int* __restrict__ block_table, int maxp, int nh, int nkv, float scale_log2, int window, const AtExtra ex) {
   using L = AtLayout<HD, AT_STAGES_PREFILL>;
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
@@ -338,13 +350,25 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     }
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  if (EX && ex.sinks) {                                       // the sink: a term exp(sink) of the denominator without a key
+    const float s0 = ex.sinks[h] * 1.4426950408889634f / (ex.cap_log2 > 0.f ? 1.f : scale_log2);
+    m[0] = m[1] = s0;
+    l[0] = l[1] = t == 0 ? 1.f : 0.f;
+  }
   float o[HD / 8][4];
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
   // pages the tile can see: from the first key visible to its first row to the last row's position
   const int first_pos = past + q0, last_pos = past + q0 + rows - 1;
-  const int lo_key = window > 0 ? max(0, first_pos - window + 1) : 0;
+  int lo_key = window > 0 ? max(0, first_pos - window + 1) : 0;
+  int low_lo = 0, low_hi = 0, warp_low = 0;                   // first keys of the chunks of this thread's rows, of the warp's first row
+  if (EX && ex.chunk > 0) {
+    lo_key = max(lo_key, (first_pos / ex.chunk) * ex.chunk);
+    low_lo = (max(pos_lo, 0) / ex.chunk) * ex.chunk;
+    low_hi = (max(pos_hi, 0) / ex.chunk) * ex.chunk;
+    warp_low = ((past + q0 + warp * 16) / ex.chunk) * ex.chunk;
+  }
   const int p0 = lo_key >> 6, p1 = (last_pos >> 6) + 1;
   const int npages = p1 - p0;
   // this warp needs pages up to its own last row only
@@ -366,7 +390,11 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     cp_async_commit();
     const unsigned char* st = smem + (i % AT_STAGES_PREFILL) * L::STAGE;
     const int jbase = (p0 + i) * 64;
-    if (warp_on && jbase <= warp_last) {
+    if (EX) {
+      if (warp_on && jbase <= warp_last && jbase + 63 >= warp_low)
+        attend_tile<HD, 8, true, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o, low_lo, low_hi,
+                                       ex.cap_log2, ex.cap_in);
+    } else if (warp_on && jbase <= warp_last) {
       // visible to every row of this warp without a comparison: ends before the warp's first row's
       // position and starts after the window's lower edge of its last row
       if (jbase + 63 > warp_first || (window > 0 && jbase <= warp_last - window))
@@ -382,9 +410,11 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
-  bf16* olo = out + ((size_t)(t_begin + q0 + r_lo) * nh + h) * HD;
-  bf16* ohi = out + ((size_t)(t_begin + q0 + r_hi) * nh + h) * HD;
+  float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  if (EX) { inv_lo *= ex.out_scale; inv_hi *= ex.out_scale; }
+  const size_t ostride = EX ? (size_t)ex.out_stride : (size_t)nh * HD;
+  bf16* olo = out + (size_t)(t_begin + q0 + r_lo) * ostride + (size_t)h * HD;
+  bf16* ohi = out + (size_t)(t_begin + q0 + r_hi) * ostride + (size_t)h * HD;
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) {
     const int c = n * 8 + 2 * t;
@@ -409,8 +439,9 @@ static int decode_launch(const bf16* q, bf16* k, bf16* v, bf16* out, float* part
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_splits, nkv, S);
+  const AtExtra no_extra = {0.f, 0.f, nullptr, 0, 0, 1.f};
   int rc = sx_launch(kern, grid, dim3(AT_THREADS), smem, stream, q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv,
-                     scale_log2, window, n_splits, counters, prep);
+                     scale_log2, window, n_splits, counters, prep, no_extra);
   if (rc || n_splits == 1 || counters) return rc;
   return sx_launch(attn_merge_kernel<HD>, dim3(S * nh), dim3(HD), 2 * n_splits * sizeof(float), stream,
                    (const float*)part_o, (const float*)part_ml, out, n_splits);
@@ -542,8 +573,84 @@ static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_tiles, nh);
+  const AtExtra no_extra = {0.f, 0.f, nullptr, 0, 0, 1.f};
   return sx_launch(kern, grid, dim3(AT_THREADS), L::SMEM, stream, q, k, v, out, tile_seq, tile_q0, cu, past, lens, bt, maxp, nh,
-                   nkv, scale_log2, window);
+                   nkv, scale_log2, window, no_extra);
+}
+
+// ---------------------------------------------------------------------------------------
+// The same two kernels with the further options of AtExtra: capped scores, a sink per head, chunks of positions, an
+// output whose rows are wider than the heads, times a factor.  The single-token form runs one split a (sequence, kv
+// head): with chunks a query sees a few pages at most.
+// ---------------------------------------------------------------------------------------
+static AtExtra make_extra(float scale, float softcap, const float* sinks, int chunk, int out_stride, float out_scale) {
+  AtExtra ex;
+  ex.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  ex.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+  ex.sinks = sinks;
+  ex.chunk = chunk;
+  ex.out_stride = out_stride;
+  ex.out_scale = out_scale;
+  return ex;
+}
+
+template <int HD>
+static int prefill_ex_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_q0,
+                             int n_tiles, const int* cu, const int* past, const int* lens, const int* bt, int maxp, int nh,
+                             int nkv, float scale_log2, int window, const AtExtra& ex, cudaStream_t stream) {
+  using L = AtLayout<HD, AT_STAGES_PREFILL>;
+  auto kern = attn_prefill_kernel<HD, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
+  if (e != cudaSuccess) return (int)e;
+  return sx_launch(kern, dim3(n_tiles, nh), dim3(AT_THREADS), L::SMEM, stream, q, k, v, out, tile_seq, tile_q0, cu, past, lens, bt,
+                   maxp, nh, nkv, scale_log2, window, ex);
+}
+
+extern "C" int sx_attn_prefill_ex(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                  const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_seqlens,
+                                  const int* seq_past, const int* seq_lens, const int* block_table, int maxp, int nh,
+                                  int nkv, int hd, float scale, int window, float softcap, const float* sinks, int chunk,
+                                  int out_stride, float out_scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || out_stride < nh * hd || (out_stride & 1) || chunk < 0) return SX_ERR_SIZE;
+  const float sl = scale * 1.4426950408889634f;
+  const AtExtra ex = make_extra(scale, softcap, sinks, chunk, out_stride, out_scale);
+  const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k_pages, *vb = (const bf16*)v_pages;
+  if (hd == 128) return prefill_ex_launch<128>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, ex, stream);
+  if (hd == 64) return prefill_ex_launch<64>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, ex, stream);
+  if (hd == 32) return prefill_ex_launch<32>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, ex, stream);
+  return SX_ERR_SIZE;
+}
+
+template <int HD>
+static int decode_ex_launch(const bf16* q, bf16* k, bf16* v, bf16* out, const int* seq_lens, const int* bt, int maxp, int S,
+                            int nh, int nkv, float scale_log2, int window, const AtExtra& ex, cudaStream_t stream) {
+  using L = AtLayout<HD>;
+  const size_t merge_bytes = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+  const size_t smem = L::SMEM > merge_bytes ? L::SMEM : merge_bytes;
+  auto kern = attn_decode_kernel<HD, false, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const AtPrep none = {nullptr, nullptr, nullptr, 0.f, 0, 0};
+  return sx_launch(kern, dim3(1, nkv, S), dim3(AT_THREADS), smem, stream, q, k, v, out, (float*)nullptr, (float*)nullptr, seq_lens,
+                   bt, maxp, nh, nkv, scale_log2, window, 1, (int*)nullptr, none, ex);
+}
+
+extern "C" int sx_attn_decode_ex(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_lens,
+                                 const int* block_table, int maxp, int S, int nh, int nkv, int hd, float scale, int window,
+                                 float softcap, const float* sinks, int chunk, int out_stride, float out_scale,
+                                 cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || nkv > 65535 || S > 65535 || out_stride < nh * hd || chunk < 0)
+    return SX_ERR_SIZE;
+  const float sl = scale * 1.4426950408889634f;
+  const AtExtra ex = make_extra(scale, softcap, sinks, chunk, out_stride, out_scale);
+  const bf16* qb = (const bf16*)q;
+  bf16 *kb = (bf16*)const_cast<void*>(k_pages), *vb = (bf16*)const_cast<void*>(v_pages), *ob = (bf16*)out;
+  if (hd == 128) return decode_ex_launch<128>(qb, kb, vb, ob, seq_lens, block_table, maxp, S, nh, nkv, sl, window, ex, stream);
+  if (hd == 64) return decode_ex_launch<64>(qb, kb, vb, ob, seq_lens, block_table, maxp, S, nh, nkv, sl, window, ex, stream);
+  if (hd == 32) return decode_ex_launch<32>(qb, kb, vb, ob, seq_lens, block_table, maxp, S, nh, nkv, sl, window, ex, stream);
+  return SX_ERR_SIZE;
 }
 
 // q [T, nh, hd] packed tokens, out [T, nh*hd]; tile_seq/tile_q0 [n_tiles] list 64-row query tiles.

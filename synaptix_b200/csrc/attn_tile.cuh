@@ -64,12 +64,25 @@ __device__ __forceinline__ void load_page(unsigned char* stage, const bf16* __re
 //   pos_lo/pos_hi  absolute positions of fragment rows g and g + 8 (keys beyond are masked);
 //                  a negative position masks the whole row
 //   jbase  absolute index of the page's first key
+// With EX (further options, see AtExtra): keys below low_lo / low_hi are masked for the two rows (the first key of the
+// row's chunk of positions), and with a cap the raw scores become cap * tanh(score * scale / cap) * log2(e) at once,
+// so that everything behind (the running maximum, the exponent) works on them with a scale of 1.
 // ---------------------------------------------------------------------------------------
-template <int HD, int NKT, bool MASKED>
+struct AtExtra {
+  float cap_log2;        // softcap * log2(e), 0: no cap
+  float cap_in;          // scale / softcap
+  const float* sinks;    // [nh] or null: exp(sink) joins the denominator of the head's softmax
+  int chunk;             // > 0: a query sees only keys of its own chunk of that many positions
+  int out_stride;        // elements between two tokens' rows of the output
+  float out_scale;       // the output is multiplied by this
+};
+
+template <int HD, int NKT, bool MASKED, bool EX = false>
 __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], const unsigned char* kst,
                                             const unsigned char* vst, int key0, int jbase, int pos_lo, int pos_hi,
                                             int window, float scale_log2, float (&m)[2], float (&l)[2],
-                                            float (&o)[HD / 8][4]) {
+                                            float (&o)[HD / 8][4], int low_lo = 0, int low_hi = 0, float cap_log2 = 0.f,
+                                            float cap_in = 0.f) {
   using L = AtLayout<HD>;
   const int lane = threadIdx.x & 31, t = lane & 3;
   float s[NKT][4];
@@ -99,6 +112,13 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
   // running maximum of the raw scores (the scale is positive, so it can be applied later inside
   // the exponent: p = 2^(s * scale - m * scale), one FFMA and one EX2 per score).  A page that lies
   // wholly inside every row's visible range (MASKED == false) needs no comparisons at all.
+  if (EX && cap_log2 > 0.f) {
+#pragma unroll
+    for (int kt = 0; kt < NKT; ++kt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[kt][e] = cap_log2 * tanhf(s[kt][e] * cap_in);
+    scale_log2 = 1.f;
+  }
   float mx[2] = {m[0], m[1]};
 #pragma unroll
   for (int kt = 0; kt < NKT; ++kt) {
@@ -107,7 +127,8 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
       if (MASKED) {
         const int j = jbase + key0 + kt * 8 + 2 * t + (e & 1);
         const int p = (e < 2) ? pos_lo : pos_hi;
-        const bool vis = j <= p && (window == 0 || j > p - window);
+        bool vis = j <= p && (window == 0 || j > p - window);
+        if (EX) vis = vis && j >= ((e < 2) ? low_lo : low_hi);
         if (!vis) s[kt][e] = -INFINITY;
       }
       mx[e >> 1] = fmaxf(mx[e >> 1], s[kt][e]);

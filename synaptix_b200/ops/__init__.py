@@ -13,7 +13,8 @@ import torch
 
 from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
-from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_decode_tma, attn_prefill, attn_prefill_tc,
+from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_ex, attn_decode_prep, attn_decode_tma, attn_prefill,
+                        attn_prefill_ex, attn_prefill_tc,
                         fast_supported, pick_splits, query_tiles, tc_prefill_supported, tma_decode_supported)
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, gemm_tc_qkv, qkv_epilogue_supported, tc_supported
@@ -263,6 +264,17 @@ def attention_from_projection(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages:
                             pick_splits(ctx.n_seqs, nkv, max_pages, qkv.device), wq, wk, inv_freq, eps, write_cache)
 
 
+def _query_tiles(ctx, rows: int, device):
+    """The step's query tiles of ``rows`` rows as two device arrays (sequence, first row), made once a step."""
+    tiles = ctx.scratch.get(("query_tiles", rows))
+    if tiles is None:
+        import numpy as np
+        ts, t0 = query_tiles(ctx.host["cu_seqlens"], rows)
+        both = torch.from_numpy(np.asarray([ts, t0], dtype=np.int32)).to(device, non_blocking=True)
+        tiles = ctx.scratch[("query_tiles", rows)] = (both[0], both[1])
+    return tiles
+
+
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor,
               nh: int, nkv: int, hd: int, scale: float, window: Optional[int], *, vd: Optional[int] = None,
               softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
@@ -273,6 +285,18 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx
     plain = (vd in (None, hd) and softcap is None and sinks is None and chunk is None and out is None
              and out_scale == 1.0)
     if not plain:
+        # the mma.sync kernels take the options when keys and values have one of their head sizes; a long window without
+        # chunks would want the single-token form's splits, which the options' form does not have
+        if (fast_supported(q.dtype, nh, nkv, hd) and vd in (None, hd) and OPTIONS.attn_options_fast
+                and (out is None or (out.shape[1] % 2 == 0 and out_col % 2 == 0))):
+            if ctx.all_single and ctx.n_seqs == q.shape[0] and (chunk is not None or ctx.max_len <= 1024):
+                return attn_decode_ex(q, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
+                                      softcap=softcap, sinks=sinks, chunk=chunk, out=out, out_col=out_col, out_scale=out_scale)
+            if not ctx.all_single and ctx.host is not None:
+                tiles = _query_tiles(ctx, 64, q.device)
+                return attn_prefill_ex(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
+                                       block_table, nh, nkv, hd, scale, window, softcap=softcap, sinks=sinks, chunk=chunk,
+                                       out=out, out_col=out_col, out_scale=out_scale)
         return attn_generic(q, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, nh, nkv, hd, scale, window,
                             out, vd=vd, softcap=softcap, sinks=sinks, chunk=chunk, out_scale=out_scale, out_col=out_col)
     if fast_supported(q.dtype, nh, nkv, hd):
@@ -286,13 +310,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx
         if ctx.host is not None:
             # prompt steps: tcgen05 kernel (128-row tiles) for head size 128, else the mma.sync kernel (64-row tiles)
             tc = tc_prefill_supported(q.dtype, nh, nkv, hd)
-            rows = TC_TILE_ROWS if tc else 64
-            tiles = ctx.scratch.get(("query_tiles", rows))
-            if tiles is None:
-                import numpy as np
-                ts, t0 = query_tiles(ctx.host["cu_seqlens"], rows)
-                both = torch.from_numpy(np.asarray([ts, t0], dtype=np.int32)).to(q.device, non_blocking=True)
-                tiles = ctx.scratch[("query_tiles", rows)] = (both[0], both[1])
+            tiles = _query_tiles(ctx, TC_TILE_ROWS if tc else 64, q.device)
             kernel = attn_prefill_tc if tc else attn_prefill
             return kernel(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
                           block_table, nh, nkv, hd, scale, window)

@@ -21,6 +21,8 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
                     rotation, cache write; else a head-preparation launch)
 ``fused_residual``  2 to 160 rows: the o / down product adds itself into the residual stream and
                     prepares the next norm
+``attn_options_fast``  attention with capped scores, sinks or chunks of positions at head size 32 / 64 / 128 in
+                    bfloat16 on the ``mma.sync`` kernels (else the plain kernel)
 ``pdl``             kernels are launched with programmatic dependent launch
 """
 from __future__ import annotations
@@ -39,6 +41,7 @@ class KernelOptions:
     gemm_ws: bool = True
     qkv_epilogue: bool = True
     fused_residual: bool = True
+    attn_options_fast: bool = True
     pdl: bool = True
 
 

@@ -30,7 +30,8 @@ def step_ctx(past, new, slots, tables=None, dtype=torch.float32):
         seq_of_token=i32([i for i, n in enumerate(new) for _ in range(n)]),
         cu_seqlens=i32(cu), seq_past=i32(past), seq_lens=i32([p + n for p, n in zip(past, new)]), seq_slots=i32(slots),
         block_tables=tables, n_tokens=sum(new), n_seqs=len(new), max_new=max(new), max_len=max(p + n for p, n in zip(past, new)),
-        all_single=all(n == 1 for n in new), runtime=Runtime(torch.device("cuda:0"), dtype))
+        all_single=all(n == 1 for n in new), runtime=Runtime(torch.device("cuda:0"), dtype),
+        host={"cu_seqlens": cu, "seq_past": list(past), "seq_lens": [p + n for p, n in zip(past, new)], "seq_slots": list(slots)})
 
 
 def portions(lengths, cuts):
@@ -185,7 +186,7 @@ def test_retention_over_portions(heads, D, E, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,vd,chunk,cap", [(4, 2, 16, 8, 10, 30.0), (2, 2, 64, 64, 100, 30.0), (4, 2, 64, 64, 37, None),
-                                                      (3, 1, 32, 48, 64, 30.0), (2, 1, 128, 128, 70, 50.0)])
+                                                      (3, 1, 32, 48, 64, 30.0), (2, 1, 128, 128, 70, 50.0), (6, 2, 32, 32, 120, 20.0)])
 def test_attention_with_chunks_cap_and_sink(nh, nkv, hd, vd, chunk, cap, dtype):
     """Softmax attention over the paged cache with chunks of positions, capped scores, a sink per head and values of their
     own size, in a prompt portion and token by token.  Keys at the first and last place of a chunk, at page borders and far
@@ -219,14 +220,22 @@ def test_attention_with_chunks_cap_and_sink(nh, nkv, hd, vd, chunk, cap, dtype):
         a = proj[past:past + new].contiguous()
         qq = torch.empty(new, nh * hd, dtype=dt).cuda()
         ops.qkv_prepare(a, qq, kp, vp, None, None, None, 0, 0.0, ctx.positions, ctx.seq_of_token, table, nh, nkv, hd, vd=vd)
-        out = torch.zeros(new, nh * vd + 3, dtype=dt).cuda()
+        oc = 4 if hd == vd else 3              # (the tensor-core kernels of bfloat16 want even columns)
+        out = torch.zeros(new, nh * vd + oc, dtype=dt).cuda()
         ops.attention(qq, kp, vp, ctx, table, nh, nkv, hd, scale, None, vd=vd, softcap=cap, sinks=sinks.cuda(), chunk=chunk,
-                      out=out, out_col=3, out_scale=2.0)
-        assert float(out[:, :3].abs().sum()) == 0.0
-        got.append(out[:, 3:].float().cpu() / 2.0)
+                      out=out, out_col=oc, out_scale=2.0)
+        assert float(out[:, :oc].abs().sum()) == 0.0
+        got.append(out[:, oc:].float().cpu() / 2.0)
     got = torch.cat(got).view(T, nh, vd)
     tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=4e-2, rtol=3e-2)
     assert torch.allclose(got.double(), ref, **tol), float((got.double() - ref).abs().max())
+    if dtype == "bfloat16" and hd == vd:           # the same through the plain kernel
+        with ops.options(attn_options_fast=False):
+            ctx = step_ctx([0], [T], [0], [table], dtype=dt)
+            qq = torch.empty(T, nh * hd, dtype=dt).cuda()
+            ops.qkv_prepare(proj, qq, kp, vp, None, None, None, 0, 0.0, ctx.positions, ctx.seq_of_token, table, nh, nkv, hd, vd=vd)
+            o2 = ops.attention(qq, kp, vp, ctx, table, nh, nkv, hd, scale, None, vd=vd, softcap=cap, sinks=sinks.cuda(), chunk=chunk)
+        assert torch.allclose(o2.float().cpu().view(T, nh, vd).double(), ref, **tol)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
