@@ -217,6 +217,102 @@ def further_points(torch, pk, graph):
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --arch vemedra: the Vemedra decoder beside the Qwen3 decoder at equal sizes (random weights): a 2,048-token prompt
+# step and decoding at batch 1 and 8, for a few widths.  Not part of the default run.
+# ---------------------------------------------------------------------------------------------------------------
+VEMEDRA_SIZES = {
+    # name: width, feed-forward, query heads, kv heads, head size, retention heads
+    "1k": (1024, 4096, 16, 4, 64, 8),
+    "2.5k": (2560, 9728, 32, 8, 128, 8),
+    "4k": (4096, 12288, 32, 8, 128, 16),
+}
+
+
+def vemedra_config(width, ff, nh, nkv, hd, rh, runs, vocab):
+    """``runs`` layer runs: layers (parallel, mingru, parallel, parallel) repeated, the first two run twice (a loop)."""
+    left = dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, softcap=50.0, mask=dict(size=1000),
+                rot=dict(dims=hd, base=250000.0))
+    right = dict(heads=rh, dim=hd, vdim=hd // 2, decay=[1.0 - 2.0 ** -(3 + i % 8) for i in range(rh)])
+    par = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=0.6, right_scale=0.5),
+               mlp=dict(kind="dense", ff=ff, limit=7.0))
+    gru = dict(type="mingru", mixer=dict(width=width), mlp=None)
+    n_layers = runs - 2
+    layers = [(gru if i % 4 == 1 else par) for i in range(n_layers)]
+    return dict(architecture="Vemedra", vocab=vocab, width=width, norm=dict(eps=1e-5), canon=dict(taps=3), layers=layers,
+                loop=dict(start=0, stop=2, times=2))
+
+
+def arch_points(torch, a):
+    from synaptix_b200.api import LLM
+    from synaptix_b200.config import Qwen3Config, VemedraConfig
+    from synaptix_b200.engine import DecodeRow, Entry
+    from synaptix_b200.models import model_skeleton
+    from synaptix_b200.parts import Runtime
+    from synaptix_b200.weights import RandomSource
+    RUNS, VOCAB, T, CONTEXT, K = 8, 32000, a.prefill_tokens, 2048, a.steps
+    g = torch.Generator().manual_seed(3)
+    out = {}
+
+    def measure(cfg, key):
+        model = model_skeleton(cfg)
+        src = RandomSource(model.all_tensor_specs(), seed=0, std_matrix=0.02, std_gain=0.05, std_bias=0.1, device="cuda:0")
+        model.load(src, Runtime(torch.device("cuda:0"), torch.bfloat16), where="random weights")
+        llm = LLM.from_model(model, max_tokens=8 * (CONTEXT + 64) + T + 64, graph=not a.no_graph)
+        engine = llm.engine
+        toks = torch.randint(0, VOCAB, (T,), generator=g).tolist()
+        times = []
+        for it in range(3 + 5):
+            s = engine.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            engine.step([Entry(s, toks, [T - 1])], keep=False)
+            e1.record()
+            torch.cuda.synchronize()
+            engine.close(s)
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+        ms = sorted(times)[len(times) // 2]
+        out[f"{key}_prefill_{T}_ms"] = round(ms, 3)
+        out[f"{key}_prefill_tok_s"] = round(T / (ms / 1e3), 1)
+        for B in (1, 8):
+            prompts = [torch.randint(0, VOCAB, (CONTEXT - 5 * K - a.warmup - 1,), generator=g).tolist() for _ in range(B)]
+            slots = [engine.open() for _ in prompts]
+            lg = engine.step([Entry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)], keep=False)
+            session = engine.start_decode([DecodeRow(s, t, i, 1) for i, (s, t) in enumerate(zip(slots, lg.argmax(-1).tolist()))])
+            events = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            for _ in range(a.warmup):
+                session.launch()
+            events[0].record()
+            for r in range(5):
+                for _ in range(K):
+                    session.launch()
+                events[r + 1].record()
+            torch.cuda.synchronize()
+            step_ms = sorted(events[r].elapsed_time(events[r + 1]) for r in range(5))[2] / K
+            for _ in range(5 * K + a.warmup):
+                session.collect()
+            session.drop(list(range(B)))
+            for s in slots:
+                engine.close(s)
+            out[f"{key}_decode_b{B}_ms"] = round(step_ms, 4)
+            out[f"{key}_decode_b{B}_tok_s"] = round(B / (step_ms / 1e3), 1)
+        del llm, engine, model, src
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    for name in (a.arch_sizes.split(",") if a.arch_sizes else list(VEMEDRA_SIZES)):
+        width, ff, nh, nkv, hd, rh = VEMEDRA_SIZES[name]
+        measure(VemedraConfig.from_dict(vemedra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"vemedra_{name}")
+        measure(Qwen3Config.from_dict(dict(QWEN3_4B, num_hidden_layers=RUNS, hidden_size=width, num_attention_heads=nh,
+                                           num_key_value_heads=nkv, head_dim=hd, intermediate_size=ff, vocab_size=VOCAB,
+                                           tie_word_embeddings=False)), f"qwen3_{name}")
+    return {"metric": "prompt step and decode step, Vemedra beside Qwen3 at equal sizes (bf16, random weights)", "impl": "ours",
+            "layer_runs": RUNS, "vocab": VOCAB, "context": CONTEXT, "steps": K, "warmup": a.warmup, "sizes": VEMEDRA_SIZES,
+            "data": "synthetic", "dtype": "bf16", "points": out}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -238,6 +334,9 @@ def main():
     ap.add_argument("--short", action="store_true",
                     help="decode only 5 x --steps + --warmup tokens instead of at least 255 (small cases for profilers: "
                          "every launch under a profiler costs a good part of a second)")
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra"],
+                    help="vemedra: the Vemedra decoder beside Qwen3 at equal sizes (prompt step, decode at batch 1 and 8) instead of the default run")
+    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra: which of 1k,2.5k,4k (default: all)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -251,6 +350,10 @@ def main():
     a.warmup = max(a.warmup, 3)
 
     import torch
+    if a.arch == "vemedra":
+        a.steps = min(a.steps, 40)
+        print(json.dumps(arch_points(torch, a)))
+        return 0
     if a.further_only:
         try:
             print(json.dumps(further_points(torch, peaks(), not a.no_graph)))

@@ -122,21 +122,21 @@ extern "C" int sx_token_conv(const float* y, const float* cw, void* out, int out
 // 256 * NC channels stay in registers.
 // ---------------------------------------------------------------------------------------
 template <typename TD, int NC>
-__global__ void __launch_bounds__(256) norm_conv_step_kernel(float* __restrict__ h, const TD* __restrict__ delta,
-                                                             const float* __restrict__ w, float eps, const float* __restrict__ cw,
-                                                             TD* __restrict__ out, float* __restrict__ hist,
-                                                             const int* __restrict__ seq_slots, int P, int H) {
+__global__ void __launch_bounds__(1024) norm_conv_step_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                                              const float* __restrict__ w, float eps, const float* __restrict__ cw,
+                                                              TD* __restrict__ out, float* __restrict__ hist,
+                                                              const int* __restrict__ seq_slots, int P, int H) {
   __shared__ float red[33];
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x;
-  float* hr = h + (size_t)t * H;
-  const TD* dr = delta ? delta + (size_t)t * H : nullptr;
+  const int t = blockIdx.x, nt = blockDim.x;
+  float* __restrict__ hr = h + (size_t)t * H;
+  const TD* __restrict__ dr = delta ? delta + (size_t)t * H : nullptr;
   float v[NC];
   float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < NC; ++k) {
-    const int c = threadIdx.x + k * 256;
+    const int c = threadIdx.x + k * nt;
     v[k] = 0.f;
     if (c < H) {
       v[k] = hr[c];
@@ -150,13 +150,13 @@ __global__ void __launch_bounds__(256) norm_conv_step_kernel(float* __restrict__
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)H + eps);
   const int taps = P + 1;
-  float* hs = hist + (size_t)seq_slots[t] * P * H;
+  float* __restrict__ hs = hist + (size_t)seq_slots[t] * P * H;
 #pragma unroll
   for (int k = 0; k < NC; ++k) {
-    const int c = threadIdx.x + k * 256;
+    const int c = threadIdx.x + k * nt;
     if (c >= H) continue;
     const float yv = v[k] * inv * w[c];
-    const float* cwc = cw + (size_t)c * taps;
+    const float* __restrict__ cwc = cw + (size_t)c * taps;
     float acc = fmaf(cwc[P], yv, yv);
     float prev = yv;                        // walks the history from the newest entry down, shifting it by one
     for (int i = P - 1; i >= 0; --i) {
@@ -172,15 +172,17 @@ __global__ void __launch_bounds__(256) norm_conv_step_kernel(float* __restrict__
 extern "C" int sx_norm_conv_step(float* h, const void* delta, const float* w, float eps, const float* cw, void* out,
                                  float* hist, const int* seq_slots, int T, int P, int H, int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (P < 0 || H <= 0 || H > 256 * 32) return SX_ERR_SIZE;
-#define NCS_GO(TD, NC)                                                                                              \
-  return sx_launch(norm_conv_step_kernel<TD, NC>, dim3(T), dim3(256), 0, stream, h, (const TD*)delta, w, eps, cw, (TD*)out, \
+  if (P < 0 || H <= 0 || H > 1024 * 8) return SX_ERR_SIZE;
+  // a token's row is one block's: as many threads as the row has channels, up to 1,024, then several channels a thread
+  const int threads = H >= 1024 ? 1024 : ((H + 31) / 32) * 32;
+#define NCS_GO(TD, NC)                                                                                                  \
+  return sx_launch(norm_conv_step_kernel<TD, NC>, dim3(T), dim3(threads), 0, stream, h, (const TD*)delta, w, eps, cw, (TD*)out, \
                    hist, seq_slots, P, H)
 #define NCS_PICK(TD)              \
-  if (H <= 256 * 4) NCS_GO(TD, 4);  \
-  if (H <= 256 * 8) NCS_GO(TD, 8);  \
-  if (H <= 256 * 16) NCS_GO(TD, 16); \
-  NCS_GO(TD, 32)
+  if (H <= threads) NCS_GO(TD, 1);     \
+  if (H <= threads * 2) NCS_GO(TD, 2); \
+  if (H <= threads * 4) NCS_GO(TD, 4); \
+  NCS_GO(TD, 8)
   if (dt == SX_F32) { NCS_PICK(float); }
   if (dt == SX_BF16) { NCS_PICK(bf16); }
 #undef NCS_PICK
@@ -427,6 +429,307 @@ extern "C" int sx_retention(const void* proj, int row, int q_off, int k_off, int
   if (dt == SX_BF16) RET_GO(bf16)
 #undef RET_GO
   return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// Retention for steps of ONE token a sequence (row t is sequence t): the state is read from and written back to
+// global memory directly, every element once, without a stop in shared memory.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) retention_step_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
+                                                             int g_off, const float* __restrict__ decay, float kscale, float eps,
+                                                             int unit_norm, float out_scale, float* __restrict__ state,
+                                                             T* __restrict__ out, int out_stride, const int* __restrict__ seq_slots,
+                                                             int heads, int D, int E) {
+  extern __shared__ float sm[];
+  float* qs = sm;            // D
+  float* ks = qs + D;        // D
+  float* part = ks + D;      // G * E
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, hd = blockIdx.y, tid = threadIdx.x;
+  const int G = blockDim.x / E, e = tid % E, g = tid / E;
+  const T* r = proj + (size_t)t * row;
+  for (int i = tid; i < D; i += blockDim.x) {
+    qs[i] = to_f32(r[q_off + hd * D + i]);
+    ks[i] = to_f32(r[k_off + hd * D + i]) * kscale;
+  }
+  __syncthreads();
+  if (g < G) {
+    const float dc = decay[hd], ve = to_f32(r[v_off + hd * E + e]);
+    float* sp = state + ((size_t)seq_slots[t] * heads + hd) * D * E + e;
+    float acc = 0.f;
+    int d = g;
+    for (; d + 3 * G < D; d += 4 * G) {                 // four rows at a time: their loads are on the way together
+      float x0 = sp[(size_t)d * E], x1 = sp[(size_t)(d + G) * E], x2 = sp[(size_t)(d + 2 * G) * E], x3 = sp[(size_t)(d + 3 * G) * E];
+      x0 = fmaf(dc, x0, ks[d] * ve); x1 = fmaf(dc, x1, ks[d + G] * ve);
+      x2 = fmaf(dc, x2, ks[d + 2 * G] * ve); x3 = fmaf(dc, x3, ks[d + 3 * G] * ve);
+      sp[(size_t)d * E] = x0; sp[(size_t)(d + G) * E] = x1; sp[(size_t)(d + 2 * G) * E] = x2; sp[(size_t)(d + 3 * G) * E] = x3;
+      acc = fmaf(x0, qs[d], acc); acc = fmaf(x1, qs[d + G], acc); acc = fmaf(x2, qs[d + 2 * G], acc); acc = fmaf(x3, qs[d + 3 * G], acc);
+    }
+    for (; d < D; d += G) {
+      const float x = fmaf(dc, sp[(size_t)d * E], ks[d] * ve);
+      sp[(size_t)d * E] = x;
+      acc = fmaf(x, qs[d], acc);
+    }
+    part[g * E + e] = acc;
+  }
+  __syncthreads();
+  float o = 0.f;
+  if (tid < E)
+    for (int i = 0; i < G; ++i) o += part[i * E + tid];
+  float inv = 1.f;
+  if (unit_norm) inv = rsqrtf(block_sum(tid < E ? o * o : 0.f, red) / (float)E + eps);
+  if (tid < E) {
+    float x = o * inv;
+    if (g_off >= 0) x *= silu_f32(to_f32(r[g_off + hd * E + tid]));
+    out[(size_t)t * out_stride + hd * E + tid] = from_f32<T>(x * out_scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Retention over long portions, in pieces of RC tokens a sequence (counted from the portion's first token), three kernels:
+//   (1) a piece's own sum U = sum_j decay^(n-1-j) k_j v_j^T (n tokens in the piece), per (piece, head, sequence);
+//   (2) the pieces' begin states one after the other: S_(c+1) = decay^n S_c + U_c, written over U; the last is the new state;
+//   (3) a piece's outputs: o_i = sum_{j<=i} decay^(i-j) (q_i . k_j) v_j + decay^(i+1) S_c^T q_i, then unit norm, gate, store.
+// All products are 32-bit FFMA on tiles in shared memory: 256 threads as 16 x 16, 4 x 4 results a thread, operands as
+// At[k][m] and B[k][n] with leading sizes that are multiples of 4 (padding zeroed), so both are read 16 bytes at a time.
+// ---------------------------------------------------------------------------------------
+#define RC 64
+__host__ __device__ static inline int up4(int x) { return (x + 3) & ~3; }
+
+template <typename F>
+__device__ __forceinline__ void tile_product2(const float* __restrict__ At1, int lda1, const float* __restrict__ B1, int ldb1, int K1,
+                                              const float* __restrict__ At2, int lda2, const float* __restrict__ B2, int ldb2, int K2,
+                                              int M4, int N4, F&& emit) {
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  for (int m0 = ty * 4; m0 < M4; m0 += 64)
+    for (int n0 = tx * 4; n0 < N4; n0 += 64) {
+      float a1[4][4], a2[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a1[i][j] = a2[i][j] = 0.f;
+#pragma unroll 4
+      for (int k = 0; k < K1; ++k) {
+        const float4 a = *reinterpret_cast<const float4*>(At1 + (size_t)k * lda1 + m0);
+        const float4 b = *reinterpret_cast<const float4*>(B1 + (size_t)k * ldb1 + n0);
+        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a1[i][j] = fmaf(av[i], bv[j], a1[i][j]);
+      }
+#pragma unroll 4
+      for (int k = 0; k < K2; ++k) {
+        const float4 a = *reinterpret_cast<const float4*>(At2 + (size_t)k * lda2 + m0);
+        const float4 b = *reinterpret_cast<const float4*>(B2 + (size_t)k * ldb2 + n0);
+        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a2[i][j] = fmaf(av[i], bv[j], a2[i][j]);
+      }
+      emit(m0, n0, a1, a2);
+    }
+}
+
+// scratch U: [S, max_pieces, heads, D * E]
+template <typename T>
+__global__ void __launch_bounds__(256) retention_piece_kernel(const T* __restrict__ proj, int row, int k_off, int v_off,
+                                                              const float* __restrict__ decay, float kscale, float* __restrict__ U,
+                                                              const int* __restrict__ cu_seqlens, int heads, int D, int E,
+                                                              int max_pieces) {
+  extern __shared__ __align__(16) float sm[];
+  pdl_wait();
+  pdl_trigger();
+  const int p = blockIdx.x, hd = blockIdx.y, s = blockIdx.z, tid = threadIdx.x;
+  const int t0 = cu_seqlens[s] + p * RC, n = min(cu_seqlens[s + 1] - t0, RC);
+  if (n <= 0) return;
+  const int D4 = up4(D), E4 = up4(E);
+  float* Kw = sm;                     // [RC][D4]: k_j * kscale * decay^(n-1-j)
+  float* V = Kw + RC * D4;            // [RC][E4]
+  const float l2 = log2f(decay[hd]);
+  for (int i = tid; i < RC * D4; i += 256) {
+    const int j = i / D4, d = i % D4;
+    Kw[i] = (j < n && d < D) ? to_f32(proj[(size_t)(t0 + j) * row + k_off + hd * D + d]) * kscale * exp2f(l2 * (float)(n - 1 - j)) : 0.f;
+  }
+  for (int i = tid; i < RC * E4; i += 256) {
+    const int j = i / E4, e = i % E4;
+    V[i] = (j < n && e < E) ? to_f32(proj[(size_t)(t0 + j) * row + v_off + hd * E + e]) : 0.f;
+  }
+  __syncthreads();
+  float* u = U + (((size_t)s * max_pieces + p) * heads + hd) * D * E;
+  tile_product2(Kw, D4, V, E4, n, Kw, D4, V, E4, 0, D4, E4, [&](int m0, int n0, float (&a1)[4][4], float (&a2)[4][4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (m0 + i < D && n0 + j < E) u[(size_t)(m0 + i) * E + n0 + j] = a1[i][j];
+  });
+}
+
+__global__ void __launch_bounds__(256) retention_carry_kernel(float* __restrict__ U, float* __restrict__ state,
+                                                              const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
+                                                              const int* __restrict__ seq_slots, int heads, int DE, int max_pieces) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.x / heads, hd = blockIdx.x % heads, i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= DE) return;
+  const int n = cu_seqlens[s + 1] - cu_seqlens[s];
+  const int pieces = (n + RC - 1) / RC;
+  const float l2 = log2f(decay[hd]);
+  float* sp = state + ((size_t)seq_slots[s] * heads + hd) * DE + i;
+  float S = *sp;
+  for (int p = 0; p < pieces; ++p) {
+    float* u = U + (((size_t)s * max_pieces + p) * heads + hd) * DE + i;
+    const float add = *u;
+    *u = S;
+    S = fmaf(exp2f(l2 * (float)min(RC, n - p * RC)), S, add);
+  }
+  *sp = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) retention_apply_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
+                                                              int g_off, const float* __restrict__ decay, float kscale, float eps,
+                                                              int unit_norm, float out_scale, const float* __restrict__ U,
+                                                              T* __restrict__ out, int out_stride, const int* __restrict__ cu_seqlens,
+                                                              int heads, int D, int E, int max_pieces) {
+  extern __shared__ __align__(16) float sm[];
+  pdl_wait();
+  pdl_trigger();
+  const int p = blockIdx.x, hd = blockIdx.y, s = blockIdx.z, tid = threadIdx.x;
+  const int t0 = cu_seqlens[s] + p * RC, n = min(cu_seqlens[s + 1] - t0, RC);
+  if (n <= 0) return;
+  const int D4 = up4(D), E4 = up4(E);
+  constexpr int LT = RC + 4;          // leading size of the transposed arrays: their stores spread over banks
+  float* Qt = sm;                     // [D][LT]   Qt[d][i] = q_i[d]
+  float* Kt = Qt + (size_t)D * LT;    // [D][LT]   Kt[d][j] = k_j[d] * kscale
+  float* V = Kt + (size_t)D * LT;     // [RC][E4]
+  float* Sb = V + RC * E4;            // [D][E4]   the state at the piece's begin
+  float* Wt = Sb + (size_t)D * E4;    // [RC][LT]  Wt[j][i] = decay^(i-j) (q_i . k_j) for j <= i, else 0
+  float* O = Wt + RC * LT;            // [RC][E4]
+  float* pw = O + RC * E4;            // [RC + 1]  decay^n
+  const float l2 = log2f(decay[hd]);
+  for (int i = tid; i <= RC; i += 256) pw[i] = exp2f(l2 * (float)i);
+  for (int i = tid; i < RC * D; i += 256) {
+    const int j = i / D, d = i % D;
+    const bool ok = j < n;
+    Qt[(size_t)d * LT + j] = ok ? to_f32(proj[(size_t)(t0 + j) * row + q_off + hd * D + d]) : 0.f;
+    Kt[(size_t)d * LT + j] = ok ? to_f32(proj[(size_t)(t0 + j) * row + k_off + hd * D + d]) * kscale : 0.f;
+  }
+  for (int i = tid; i < D * 4; i += 256) {            // the padding columns RC .. RC+3 of both
+    Qt[(size_t)(i / 4) * LT + RC + (i % 4)] = 0.f;
+    Kt[(size_t)(i / 4) * LT + RC + (i % 4)] = 0.f;
+  }
+  for (int i = tid; i < RC * E4; i += 256) {
+    const int j = i / E4, e = i % E4;
+    V[i] = (j < n && e < E) ? to_f32(proj[(size_t)(t0 + j) * row + v_off + hd * E + e]) : 0.f;
+  }
+  const float* u = U + (((size_t)s * max_pieces + p) * heads + hd) * D * E;
+  for (int i = tid; i < D * E4; i += 256) {
+    const int d = i / E4, e = i % E4;
+    Sb[i] = e < E ? u[(size_t)d * E + e] : 0.f;
+  }
+  __syncthreads();
+  // Wt[j][i]: the product over d with m = j and n = i
+  tile_product2(Kt, LT, Qt, LT, D, Kt, LT, Qt, LT, 0, RC, RC, [&](int m0, int n0, float (&a1)[4][4], float (&a2)[4][4]) {
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int j = m0 + a, i = n0 + b;
+        Wt[j * LT + i] = (i >= j) ? a1[a][b] * pw[i - j] : 0.f;
+      }
+  });
+  __syncthreads();
+  // O[i][e] = sum_j Wt[j][i] V[j][e] + decay^(i+1) sum_d Qt[d][i] Sb[d][e]
+  tile_product2(Wt, LT, V, E4, n, Qt, LT, Sb, E4, D, RC, E4, [&](int m0, int n0, float (&a1)[4][4], float (&a2)[4][4]) {
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) O[(m0 + a) * E4 + n0 + b] = fmaf(pw[m0 + a + 1], a2[a][b], a1[a][b]);
+  });
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int i = warp; i < n; i += 8) {
+    float ss = 0.f;
+    for (int e = lane; e < E; e += 32) ss += O[i * E4 + e] * O[i * E4 + e];
+    const float inv = unit_norm ? rsqrtf(warp_sum(ss) / (float)E + eps) : 1.f;
+    const T* r = proj + (size_t)(t0 + i) * row;
+    for (int e = lane; e < E; e += 32) {
+      float x = O[i * E4 + e] * inv;
+      if (g_off >= 0) x *= silu_f32(to_f32(r[g_off + hd * E + e]));
+      out[(size_t)(t0 + i) * out_stride + hd * E + e] = from_f32<T>(x * out_scale);
+    }
+  }
+}
+
+static size_t retention_apply_smem(int D, int E) {
+  const int E4 = up4(E), LT = RC + 4;
+  return ((size_t)2 * D * LT + (size_t)RC * E4 * 2 + (size_t)D * E4 + (size_t)RC * LT + RC + 4) * sizeof(float);
+}
+// can the long-portion form run for these sizes?  (its tiles have to fit an SM's shared memory)
+extern "C" int sx_retention_pieces_fit(int D, int E) { return retention_apply_smem(D, E) <= 200 * 1024 ? 1 : 0; }
+extern "C" int sx_retention_piece_tokens() { return RC; }
+
+template <typename T>
+static int retention_pieces_launch(const void* proj, int row, int q_off, int k_off, int v_off, int g_off, const float* decay,
+                                   float kscale, float eps, int unit_norm, float out_scale, float* state, void* out,
+                                   int out_stride, float* scratch, const int* cu_seqlens, const int* seq_slots, int S, int heads,
+                                   int D, int E, int max_new, cudaStream_t stream) {
+  const int max_pieces = (max_new + RC - 1) / RC;
+  const size_t smem1 = ((size_t)RC * up4(D) + (size_t)RC * up4(E)) * sizeof(float);
+  const size_t smem3 = retention_apply_smem(D, E);
+  cudaError_t ce = cudaFuncSetAttribute(retention_piece_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+  if (ce != cudaSuccess) return (int)ce;
+  ce = cudaFuncSetAttribute(retention_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+  if (ce != cudaSuccess) return (int)ce;
+  const dim3 grid(max_pieces, heads, S);
+  int e = sx_launch(retention_piece_kernel<T>, grid, dim3(256), smem1, stream, (const T*)proj, row, k_off, v_off, decay, kscale,
+                    scratch, cu_seqlens, heads, D, E, max_pieces);
+  if (e) return e;
+  e = sx_launch(retention_carry_kernel, dim3(S * heads, (D * E + 255) / 256), dim3(256), 0, stream, scratch, state, decay, cu_seqlens,
+                seq_slots, heads, D * E, max_pieces);
+  if (e) return e;
+  return sx_launch(retention_apply_kernel<T>, grid, dim3(256), smem3, stream, (const T*)proj, row, q_off, k_off, v_off, g_off, decay,
+                   kscale, eps, unit_norm, out_scale, (const float*)scratch, (T*)out, out_stride, cu_seqlens, heads, D, E, max_pieces);
+}
+
+// mode 0: one block a (sequence, head) walks the tokens;  mode 1: single-token steps (row t is sequence t);
+// mode 2: pieces (scratch float32 [S, ceil(max_new / 64), heads, D * E])
+extern "C" int sx_retention_any(const void* proj, int row, int q_off, int k_off, int v_off, int g_off, const float* decay,
+                                float kscale, float eps, int unit_norm, float out_scale, float* state, void* out, int out_stride,
+                                float* scratch, const int* cu_seqlens, const int* seq_slots, int S, int heads, int D, int E,
+                                int max_new, int mode, int dt, cudaStream_t stream) {
+  if (S <= 0 || heads <= 0) return 0;
+  if (D <= 0 || E <= 0 || E > 256 || heads > 65535 || S > 65535) return SX_ERR_SIZE;
+  if (mode == 2) {
+    if (!scratch || !sx_retention_pieces_fit(D, E)) return SX_ERR_SIZE;
+    if (dt == SX_F32)
+      return retention_pieces_launch<float>(proj, row, q_off, k_off, v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, out,
+                                            out_stride, scratch, cu_seqlens, seq_slots, S, heads, D, E, max_new, stream);
+    if (dt == SX_BF16)
+      return retention_pieces_launch<bf16>(proj, row, q_off, k_off, v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, out,
+                                           out_stride, scratch, cu_seqlens, seq_slots, S, heads, D, E, max_new, stream);
+    return SX_ERR_DTYPE;
+  }
+  if (mode == 1) {
+    const int G = 256 / E;
+    const size_t smem = ((size_t)2 * D + (size_t)G * E) * sizeof(float);
+    if (smem > 48 * 1024) return SX_ERR_SIZE;
+    if (dt == SX_F32)
+      return sx_launch(retention_step_kernel<float>, dim3(S, heads), dim3(256), smem, stream, (const float*)proj, row, q_off, k_off,
+                       v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, (float*)out, out_stride, seq_slots, heads, D, E);
+    if (dt == SX_BF16)
+      return sx_launch(retention_step_kernel<bf16>, dim3(S, heads), dim3(256), smem, stream, (const bf16*)proj, row, q_off, k_off,
+                       v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, (bf16*)out, out_stride, seq_slots, heads, D, E);
+    return SX_ERR_DTYPE;
+  }
+  return sx_retention(proj, row, q_off, k_off, v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, out, out_stride,
+                      cu_seqlens, seq_slots, S, heads, D, E, dt, stream);
 }
 
 // ---------------------------------------------------------------------------------------

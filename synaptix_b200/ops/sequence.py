@@ -54,6 +54,9 @@ def add_rmsnorm_conv(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch
 
 _PIECE = [0]
 
+# portions of at least this many tokens (the longest of a step) run retention in pieces
+PIECES_MIN_TOKENS = 48
+
 
 def mingru(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, n: int, bias_z: Optional[torch.Tensor],
            bias_x: Optional[torch.Tensor], state: torch.Tensor, ctx) -> torch.Tensor:
@@ -98,12 +101,21 @@ def retention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: Opt
     if out.dtype != proj.dtype or out_col + heads * vdim > out.shape[1] or not out.is_contiguous():
         raise KernelError("retention: the output does not fit")
     o = out if out_col == 0 else out.view(-1)[out_col:]
-    check(fn("sequence", "sx_retention")(ptr(proj), c_int(row), c_int(q_off), c_int(k_off), c_int(v_off),
-                                         c_int(-1 if g_off is None else g_off), ptr(decay), c_float(k_scale), c_float(eps),
-                                         c_int(1 if unit_norm else 0), c_float(out_scale), ptr(state),
-                                         ptr(o), c_int(out.shape[1]), ptr(ctx.cu_seqlens), ptr(ctx.seq_slots),
-                                         c_int(ctx.n_seqs), c_int(heads), c_int(dim), c_int(vdim), c_int(dt_code(proj.dtype)),
-                                         stream()), "retention")
+    # single tokens: the state goes through registers; long portions: pieces of 64 tokens (three kernels); else a block
+    # a (sequence, head) walks the tokens
+    mode, scratch, launches = 0, None, 1
+    if ctx.all_single and ctx.n_seqs == T and 2 * dim + 256 <= 12 * 1024:
+        mode = 1
+    elif ctx.max_new >= PIECES_MIN_TOKENS and fn("sequence", "sx_retention_pieces_fit")(c_int(dim), c_int(vdim)):
+        mode, launches = 2, 3
+        pieces = (ctx.max_new + 63) // 64
+        scratch = torch.empty((ctx.n_seqs, pieces, heads, dim * vdim), dtype=torch.float32, device=proj.device)
+    check(fn("sequence", "sx_retention_any")(ptr(proj), c_int(row), c_int(q_off), c_int(k_off), c_int(v_off),
+                                             c_int(-1 if g_off is None else g_off), ptr(decay), c_float(k_scale), c_float(eps),
+                                             c_int(1 if unit_norm else 0), c_float(out_scale), ptr(state),
+                                             ptr(o), c_int(out.shape[1]), ptr(scratch), ptr(ctx.cu_seqlens), ptr(ctx.seq_slots),
+                                             c_int(ctx.n_seqs), c_int(heads), c_int(dim), c_int(vdim), c_int(ctx.max_new),
+                                             c_int(mode), c_int(dt_code(proj.dtype)), stream()), "retention", launches=launches)
     return out
 
 
