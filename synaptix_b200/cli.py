@@ -173,7 +173,16 @@ def cmd_inspect(a) -> int:
         cfg = load_config(path)
         d = cfg.to_dict()
         print(f"=== model folder: {path} ===")
-        print(f"  architecture: {(d.get('architectures') or ['?'])[0]} ({d.get('model_type', '?')})")
+        print(f"  architecture: {type(cfg).architectures[0]} ({d.get('model_type', type(cfg).model_types[0] if type(cfg).model_types else '?')})")
+        if isinstance(d.get("layers"), list):              # a configuration that lists its layers: the scalars, then a line a layer
+            for k, v in d.items():
+                if isinstance(v, (int, float, str)) and k != "architecture":
+                    print(f"  {k}: {v}")
+                elif isinstance(v, dict) and all(isinstance(x, (int, float, str)) for x in v.values()):
+                    print(f"  {k}: " + ", ".join(f"{kk} {vv}" for kk, vv in v.items()))
+            for i, layer in enumerate(d["layers"]):
+                ff = layer.get("mlp")
+                print(f"  layer {i}: {layer.get('type')}" + (f", feed-forward {ff.get('ff')}" if isinstance(ff, dict) else ", no feed-forward"))
         for k in ("num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
                   "intermediate_size", "vocab_size", "rope_theta", "rms_norm_eps", "tie_word_embeddings",
                   "max_position_embeddings"):

@@ -167,4 +167,23 @@ __device__ __forceinline__ float cluster_load_f32(const float* local, uint32_t r
   return v;
 }
 
+// ---------------------------------------------------------------------------------------
+// The gated activation that the products of a stacked [gate; up] matrix apply in their epilogues:
+//   limit <= 0:  silu(g) * u                                              (SwiGLU)
+//   limit >  0:  g' sigmoid(alpha g') (u' + 1),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+// The choice is a value of the library (sx_set_gate_act), read when a product is launched and handed to its kernel by
+// value, so a launch recorded into a CUDA graph keeps the activation it was recorded with.
+// ---------------------------------------------------------------------------------------
+struct GateAct { float alpha, limit; };
+__device__ __forceinline__ float gate_mul(float g, float u, const GateAct a) {
+  if (a.limit > 0.f) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.f + __expf(-a.alpha * g)) * (u + 1.f);
+  }
+  return g / (1.f + __expf(-g)) * u;
+}
+static GateAct g_sx_gate = {0.f, 0.f};
+extern "C" void sx_set_gate_act(float alpha, float limit) { g_sx_gate.alpha = alpha; g_sx_gate.limit = limit; }
+
 #define SX_PAGE 64

@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
     const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
     // norm prologue (XS only): x = rmsnorm(h_in + delta) * gain; block 0 writes h_in + delta to h_out
     const float* __restrict__ h_in, const bf16* __restrict__ delta, float* __restrict__ h_out,
-    const float* __restrict__ gain, float eps, const SkNorm nrm) {
+    const float* __restrict__ gain, float eps, const SkNorm nrm, const GateAct act) {
   constexpr int WARPS = KS > SK_WARPS ? KS : SK_WARPS;      // 16 warps split K for matrices with few rows
   constexpr int THREADS = WARPS * 32;
   constexpr int RT = WARPS / KS;
@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
         const int i = tile * 8 + g;
         if (i < I) {
           const float gate = acc[nt][j], up = acc[nt][2 + j];
-          reinterpret_cast<bf16*>(out)[(size_t)b * I + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+          reinterpret_cast<bf16*>(out)[(size_t)b * I + i] = __float2bfloat16_rn(gate_mul(gate, up, act));
         }
       } else {
         const int n0 = tile * 16 + g, n1 = n0 + 8;
@@ -405,7 +405,7 @@ static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return sx_launch(kern, dim3(grid), dim3(THREADS), smem, stream, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm);
+  return sx_launch(kern, dim3(grid), dim3(THREADS), smem, stream, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, g_sx_gate);
 }
 
 // 8 warps split K, or 16 (blocks of 16 warps); 1, 2 and 4 measured slower everywhere and are not built

@@ -63,7 +63,7 @@ template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_w,
                                                                 void* __restrict__ out, int M, int N, int K,
-                                                                int* __restrict__ status) {
+                                                                int* __restrict__ status, const GateAct act) {
   constexpr int TC_BN = BN, TC_STAGES = TcShape<BN>::STAGES, TC_B_BYTES = TcShape<BN>::B_BYTES,
                 TC_STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           f[i] = __uint_as_float(v[i]);
-          if (EPI == TC_EPI_SILU_MUL) f[i] = f[i] / (1.f + expf(-f[i])) * __uint_as_float(u[i]);
+          if (EPI == TC_EPI_SILU_MUL) f[i] = gate_mul(f[i], __uint_as_float(u[i]), act);
         }
         const int ncol = min(32, n_out - (n0 + c0));
         if (EPI == TC_EPI_F32 || EPI == TC_EPI_PARTIAL) {
@@ -216,12 +216,12 @@ __device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
 
 template <int EPI>
 __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], const uint32_t (&u)[32], void* __restrict__ out,
-                                               int row, int col, int n_out) {
+                                               int row, int col, int n_out, const GateAct act) {
   float f[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     f[i] = __uint_as_float(v[i]);
-    if (EPI == TC_EPI_SILU_MUL) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
+    if (EPI == TC_EPI_SILU_MUL) f[i] = gate_mul(f[i], __uint_as_float(u[i]), act);
   }
   const int ncol = min(32, n_out - col);
   if (EPI == TC_EPI_F32) {
@@ -315,7 +315,8 @@ __global__ void __launch_bounds__(TcThreads<EPI>::N, 1) gemm_tc_persistent_kerne
                                                                            int n_whole, int zmax, int sp,
                                                                            float* __restrict__ piece_ws,
                                                                            int* __restrict__ piece_count,
-                                                                           int* __restrict__ status, const TcQkv qk) {
+                                                                           int* __restrict__ status, const TcQkv qk,
+                                                                           const GateAct act) {
   constexpr int STAGES = TcShape<BN>::STAGES, B_BYTES = TcShape<BN>::B_BYTES, STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -546,7 +547,7 @@ __global__ void __launch_bounds__(TcThreads<EPI>::N, 1) gemm_tc_persistent_kerne
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
           }
-          if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+          if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out, act);
         }
       }
       return true;
@@ -660,7 +661,7 @@ __global__ void __launch_bounds__(TcThreads<EPI>::N, 1) gemm_tc_persistent_kerne
             if (EPI == TC_EPI_SILU_MUL) {
               const float u[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) o[j] = o[j] / (1.f + __expf(-o[j])) * u[j];
+              for (int j = 0; j < 4; ++j) o[j] = gate_mul(o[j], u[j], act);
             }
             const size_t at = (size_t)r * n_out + n0 + c4;
             const bool vec = c4 + 3 < cols && (n_out & 3) == 0;
@@ -731,7 +732,7 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, in
   auto kern = gemm_tc_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, status);
+  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, status, g_sx_gate);
 }
 
 static int tc_sm_count() {
@@ -748,7 +749,7 @@ static int tc_sm_count() {
 // four columns).  Used when the persistent kernel had no whole tiles to hide its own adding-up behind.
 template <int EPI, int BN>
 __global__ void tc_pieces_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int M, int N, int n_whole,
-                                        int R, int nkb, int G, int zmax, int sp) {
+                                        int R, int nkb, int G, int zmax, int sp, const GateAct act) {
   pdl_wait();
   pdl_trigger();
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
@@ -783,7 +784,7 @@ __global__ void tc_pieces_reduce_kernel(const float* __restrict__ ws, void* __re
   if (EPI == TC_EPI_SILU_MUL) {
     const float u[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] = o[j] / (1.f + __expf(-o[j])) * u[j];
+    for (int j = 0; j < 4; ++j) o[j] = gate_mul(o[j], u[j], act);
   }
   const size_t at = (size_t)r * n_out + n0 + c4;
   const bool vec = c4 + 3 < cols && (n_out & 3) == 0;
@@ -917,19 +918,19 @@ static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, vo
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   // with whole tiles after them, the blocks of a cut tile add up inside the kernel; without, a second kernel does
-  int rc = sx_launch(kern, h.G, dim3(TcThreads<EPI>::N), smem, stream, ma, mw, out, M, N, K, h.n_whole, h.zmax, h.sp, ws, counts, status, qk);
+  int rc = sx_launch(kern, h.G, dim3(TcThreads<EPI>::N), smem, stream, ma, mw, out, M, N, K, h.n_whole, h.zmax, h.sp, ws, counts, status, qk, g_sx_gate);
   if (rc || h.R == 0 || h.sp > 0 || EPI == TC_EPI_QKV) return rc;
   const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
   const long long total = (long long)h.R * TC_BM * (tile_n / 4);
   return sx_launch(tc_pieces_reduce_kernel<EPI, BN>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const float*)ws, out,
-                   M, N, h.n_whole, h.R, (K + TC_BK - 1) / TC_BK, h.G, h.zmax, 0);
+                   M, N, h.n_whole, h.R, (K + TC_BK - 1) / TC_BK, h.G, h.zmax, 0, g_sx_gate);
 }
 
 // sum of the split-K partial tiles ws[splits][M][N] in split order, then the epilogue
 template <int EPI>
 // (out has rows of ldo values: a block of a larger matrix when ldo > the block's width)
 __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int splits, int M, int N,
-                                        long long ldo) {
+                                        long long ldo, const GateAct act) {
   pdl_wait();
   pdl_trigger();
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
@@ -944,7 +945,7 @@ __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __re
     if (EPI == TC_EPI_SILU_MUL) b += ws[z * plane + m * N + n_out + n];
   }
   const size_t o = m * (size_t)ldo + n;
-  if (EPI == TC_EPI_SILU_MUL) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(a / (1.f + expf(-a)) * b);
+  if (EPI == TC_EPI_SILU_MUL) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(gate_mul(a, b, act));
   else if (EPI == TC_EPI_F32) reinterpret_cast<float*>(out)[o] = a;
   else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(a);
 }
@@ -966,9 +967,9 @@ static int tc_split_product(const void* A, const void* W, void* out, int M, int 
   const size_t n_elems = (size_t)M * (epi == TC_EPI_SILU_MUL ? N / 2 : N);
   const unsigned grid = (unsigned)((n_elems + 255) / 256);
   switch (epi) {
-    case TC_EPI_BF16: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_BF16>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo);
-    case TC_EPI_F32: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_F32>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo);
-    case TC_EPI_SILU_MUL: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_SILU_MUL>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo);
+    case TC_EPI_BF16: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_BF16>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo, g_sx_gate);
+    case TC_EPI_F32: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_F32>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo, g_sx_gate);
+    case TC_EPI_SILU_MUL: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_SILU_MUL>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo, g_sx_gate);
     default: return SX_ERR_DTYPE;
   }
 }

@@ -41,6 +41,7 @@ struct WsEpilogue {
   float* h;              // residual stream [M, N] (WS_EPI_RESIDUAL)
   const float* gain;     // [N]
   float* ssq_out;        // [M, tiles * splits]
+  GateAct act;              // the gated activation of the SiLU-mul epilogue's place (see common.cuh)
 };
 
 __device__ __forceinline__ float4 ws_cluster_load4(const float* local, uint32_t rank) {
@@ -308,8 +309,7 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
         const float u[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float g = o[j] * rf;
-          o[j] = g / (1.f + __expf(-g)) * (u[j] * rf);
+          o[j] = gate_mul(o[j] * rf, u[j] * rf, ep.act);
         }
       } else {
 #pragma unroll
@@ -503,6 +503,7 @@ extern "C" int sx_gemm_ws(const void* X, const void* W, void* out, int M, int N,
   while (splits > nkb) splits /= 2;
   WsEpilogue ep;
   ep.ssq_in = ssq_in; ep.n_ssq = n_ssq; ep.eps = eps; ep.h = h; ep.gain = gain; ep.ssq_out = ssq_out;
+  ep.act = g_sx_gate;
   switch (epi) {
     case WS_EPI_BF16: return ws_launch<WS_EPI_BF16>(X, W, out, M, N, K, splits, stages, ep, stream);
     case WS_EPI_F32: return ws_launch<WS_EPI_F32>(X, W, out, M, N, K, splits, stages, ep, stream);

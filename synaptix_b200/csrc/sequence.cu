@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ 
   float* sp = state + (size_t)seq_slots[s] * N + c;
   float S = *sp;
   const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
+#pragma unroll 4
   for (int t = t0; t < t1; ++t) {
     const T* r = proj + (size_t)t * row;
     float keep, add;
@@ -236,13 +237,9 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ 
 }
 
 #define MG_CH 64
-// pieces are counted over the packed stream: piece p covers tokens p*CH .. p*CH+CH-1, cut at sequence borders, so a
-// piece may hold the end of one sequence and the beginning of the next; (A, B) are kept per (piece, part) with part 0
-// = the tokens of the sequence the piece begins in, part 1.. the following sequences (each begins a sequence, so its
-// begin state is that sequence's carried state).  To keep this simple a piece never crosses a border: the host-free
-// way to get that is to cut every SEQUENCE into pieces of its own: piece index = piece_base[s] + k.  piece_base is
-// not known on the device without a scan, so the grid is (max pieces of a sequence, S) and pieces beyond a
-// sequence's end return at once.
+// every SEQUENCE is cut into pieces of its own (piece k of sequence s covers its tokens 64 k .. 64 k + 63 of this step),
+// so no piece crosses a border between sequences; the grid is (most pieces of a sequence, sequences, channel blocks) and
+// pieces beyond a sequence's end return at once.  AB: [S, max_pieces, 2, N].
 template <typename T>
 __global__ void __launch_bounds__(128) mingru_piece_kernel(const T* __restrict__ proj, int row, int z_off, int x_off,
                                                            const float* __restrict__ bz, const float* __restrict__ bx,
@@ -255,6 +252,7 @@ __global__ void __launch_bounds__(128) mingru_piece_kernel(const T* __restrict__
   if (c >= N || t0 >= t1) return;
   const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
   float A = 1.f, B = 0.f;
+#pragma unroll 4
   for (int t = t0; t < t1; ++t) {
     float keep, add;
     mingru_gate(proj + (size_t)t * row, z_off, x_off, c, b_z, b_x, keep, add);
@@ -299,6 +297,7 @@ __global__ void __launch_bounds__(128) mingru_apply_kernel(const T* __restrict__
   if (c >= N || t0 >= t1) return;
   const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
   float S = AB[(((size_t)s * max_pieces + p) * 2) * N + c];
+#pragma unroll 4
   for (int t = t0; t < t1; ++t) {
     const T* r = proj + (size_t)t * row;
     float keep, add;

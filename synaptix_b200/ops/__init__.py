@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from ..csrc.build import KernelsUnavailable
-from ._lib import KernelError, set_launch_counter
+from ._lib import KernelError, current_gate, gate_activation, set_launch_counter
 from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_ex, attn_decode_prep, attn_decode_tma, attn_prefill,
                         attn_prefill_ex, attn_prefill_tc,
                         fast_supported, pick_splits, query_tiles, tc_prefill_supported, tma_decode_supported)
@@ -28,7 +28,7 @@ __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavail
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
            "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table",
-           "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add"]
+           "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add", "gate_activation"]
 
 
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
@@ -121,7 +121,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
            epilogue: Optional[str] = None) -> torch.Tensor:
     """``x[M, K] @ w[N, K].T`` with 32-bit accumulation; output in ``out_dtype`` (default ``x``'s).
     ``epilogue="silu_mul"``: ``w`` is ``[gate; up]`` stacked and the result is
-    ``silu(x gate^T) * (x up^T)``, ``[M, N/2]``."""
+    ``silu(x gate^T) * (x up^T)``, ``[M, N/2]``; inside ``gate_activation(alpha, limit)`` it is the capped form
+    ``g sigmoid(alpha g) (u + 1)`` with ``g = min(x gate^T, limit)``, ``u = clamp(x up^T, -limit, limit)`` instead."""
     M, K = x.shape
     N = w.shape[0]
     if out_dtype is None:
@@ -144,7 +145,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             return gemm_tc(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
     y = gemm_generic(x, w, out_dtype=out_dtype if epilogue is None else x.dtype)
     if epilogue == "silu_mul":
-        y = silu_mul(y)
+        alpha, limit = current_gate()            # which gated activation the epilogue stands for (see gate_activation)
+        y = capped_glu(y, alpha, limit) if limit > 0 else silu_mul(y)
     return y
 
 

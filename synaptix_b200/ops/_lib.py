@@ -1,6 +1,7 @@
 """Calling the compiled kernels: pointers, dtype codes, streams, error codes."""
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Optional
 
@@ -122,3 +123,36 @@ c_int = ctypes.c_int
 c_float = ctypes.c_float
 c_longlong = ctypes.c_longlong
 c_ulonglong = ctypes.c_ulonglong
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The gated activation of the products' "silu_mul" epilogue.  (0, 0) is silu(g) * u; (alpha, limit) with limit > 0 is
+# g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).  A feed-forward that wants the
+# second form runs its gate/up product inside ``gate_activation(alpha, limit)``; the faces of the products call
+# ``use_gate`` before a launch with that epilogue, which tells the library if its last value was another one.
+# ---------------------------------------------------------------------------------------------------------------
+_GATE = [(0.0, 0.0)]
+_LIB_GATE = {}
+
+
+@contextlib.contextmanager
+def gate_activation(alpha: float, limit: float):
+    old = _GATE[0]
+    _GATE[0] = (float(alpha), float(limit))
+    try:
+        yield
+    finally:
+        _GATE[0] = old
+
+
+def current_gate():
+    return _GATE[0]
+
+
+def use_gate(lib: str) -> None:
+    want = _GATE[0]
+    if _LIB_GATE.get(lib) != want:
+        f = getattr(_library(lib), "sx_set_gate_act")
+        f.restype = None
+        f(ctypes.c_float(want[0]), ctypes.c_float(want[1]))
+        _LIB_GATE[lib] = want

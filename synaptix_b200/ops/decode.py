@@ -5,7 +5,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream
+from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream, use_gate
 
 _EPI = {None: 0, "f32": 1, "silu_mul": 2}
 MAX_ROWS = 16          # more rows go to the tcgen05 product, which takes every K this kernel takes
@@ -54,6 +54,8 @@ def skinny_gemm(x: Optional[torch.Tensor], w: torch.Tensor, *, epilogue: Optiona
     tiles = (n_out + 7) // 8 if epilogue == "silu_mul" else (N + 15) // 16
     if ks is None:
         ks = pick_ks(tiles, K)
+    if epilogue == "silu_mul":
+        use_gate("decode")
     check(fn("decode", "sx_skinny_gemm")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
                                          c_int(ks), ptr(norm_h), ptr(norm_delta), ptr(norm_h_out), ptr(norm_gain),
                                          c_float(norm_eps), stream()), "skinny_gemm")
@@ -76,6 +78,8 @@ def skinny_gemm_scaled(x: torch.Tensor, w: torch.Tensor, ssq: Optional[torch.Ten
     tiles = (n_out + 7) // 8 if epilogue == "silu_mul" else (N + 15) // 16
     if ks is None:
         ks = pick_ks(tiles, K)
+    if epilogue == "silu_mul":
+        use_gate("decode")
     check(fn("decode", "sx_skinny_gemm_norm")(
         ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]), c_int(ks), ptr(ssq),
         c_int(0 if ssq is None else ssq.shape[1]), c_float(eps), ptr(None), ptr(None), ptr(None), stream()),

@@ -6,7 +6,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import KernelError, c_int, check, fn, ptr, require_cuda, stream
+from ._lib import KernelError, c_int, check, fn, ptr, require_cuda, stream, use_gate
 from .decode import sm_count
 from .options import OPTIONS
 
@@ -111,6 +111,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     if epilogue not in _EPI:
         raise KernelError(f"gemm_tc: unknown epilogue {epilogue!r}")
     n_out = N // 2 if epilogue == "silu_mul" else N
+    if epilogue == "silu_mul":
+        use_gate("gemm_tc")
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
     ws = counts = None

@@ -6,7 +6,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream
+from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream, use_gate
 
 _EPI = {None: 0, "f32": 1, "silu_mul": 2, "residual": 3}
 MAX_ROWS = 256
@@ -51,6 +51,8 @@ def gemm_ws(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     n_out = N // 2 if epilogue == "silu_mul" else N
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
+    if epilogue == "silu_mul":
+        use_gate("gemm_ws")
     check(fn("gemm_ws", "sx_gemm_ws")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
                                       c_int(splits or 0), c_int(stages or 0), ptr(ssq), c_int(0 if ssq is None else ssq.shape[1]),
                                       c_float(eps), ptr(None), ptr(None), ptr(None), stream()), "gemm_ws")

@@ -53,5 +53,6 @@ class CappedGLU(FeedForward):
         return [self.gate_up, self.down]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, defer_output: bool = False) -> torch.Tensor:
-        z = ops.capped_glu(self.gate_up.forward(x), self.alpha, self.limit)
+        with ops.gate_activation(self.alpha, self.limit):          # the gate/up product's epilogue applies it
+            z = self.gate_up.forward(x, epilogue="silu_mul")
         return self.down.deferred(z) if defer_output else self.down.forward(z)

@@ -259,6 +259,29 @@ def test_capped_gated_activation_and_stream_sums(dtype):
     assert torch.allclose(hd.cpu(), h + vec, atol=1e-6)
 
 
+@pytest.mark.parametrize("rows", [1, 2, 8, 16, 40, 160, 300, 700])
+def test_capped_gated_activation_in_the_products_epilogues(rows):
+    """Every bfloat16 product with the gated epilogue (the weight-streaming ones of few rows, the tile product of prompt
+    steps with its cut tiles) applies the capped form inside ``gate_activation`` and SiLU * up outside of it."""
+    from synaptix_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    K, I = 256, 640
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, generator=g) * 0.15).to(torch.bfloat16)
+    a = x.double() @ w.double().T
+    gate, up = torch.clamp(a[:, :I], max=1.25), torch.clamp(a[:, I:], -1.25, 1.25)
+    capped = gate * torch.sigmoid(1.702 * gate) * (up + 1)
+    plain = torch.nn.functional.silu(a[:, :I]) * a[:, I:]
+    with ops.gate_activation(1.702, 1.25):
+        got = ops.linear(x.cuda(), w.cuda(), epilogue="silu_mul").float().cpu().double()
+    assert torch.allclose(got, capped, atol=3e-2, rtol=2e-2), float((got - capped).abs().max())
+    got = ops.linear(x.cuda(), w.cuda(), epilogue="silu_mul").float().cpu().double()
+    assert torch.allclose(got, plain, atol=6e-2, rtol=2e-2), float((got - plain).abs().max())
+    with ops.gate_activation(1.702, 1.25):                   # and in 32-bit, through the plain kernels
+        got = ops.linear(x.float().cuda(), w.float().cuda(), epilogue="silu_mul").cpu().double()
+    assert torch.allclose(got, capped, atol=1e-4, rtol=1e-4)
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # whole models through the engine
 # ---------------------------------------------------------------------------------------------------------------
