@@ -362,12 +362,13 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
   // pages the tile can see: from the first key visible to its first row to the last row's position
   const int first_pos = past + q0, last_pos = past + q0 + rows - 1;
   int lo_key = window > 0 ? max(0, first_pos - window + 1) : 0;
-  int low_lo = 0, low_hi = 0, warp_low = 0;                   // first keys of the chunks of this thread's rows, of the warp's first row
+  int low_lo = 0, low_hi = 0, warp_low = 0, warp_low_last = 0;   // first keys of the chunks of this thread's rows, of the warp's first and last row
   if (EX && ex.chunk > 0) {
     lo_key = max(lo_key, (first_pos / ex.chunk) * ex.chunk);
     low_lo = (max(pos_lo, 0) / ex.chunk) * ex.chunk;
     low_hi = (max(pos_hi, 0) / ex.chunk) * ex.chunk;
     warp_low = ((past + q0 + warp * 16) / ex.chunk) * ex.chunk;
+    warp_low_last = ((past + q0 + min(rows - 1, warp * 16 + 15)) / ex.chunk) * ex.chunk;
   }
   const int p0 = lo_key >> 6, p1 = (last_pos >> 6) + 1;
   const int npages = p1 - p0;
@@ -391,9 +392,16 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     const unsigned char* st = smem + (i % AT_STAGES_PREFILL) * L::STAGE;
     const int jbase = (p0 + i) * 64;
     if (EX) {
-      if (warp_on && jbase <= warp_last && jbase + 63 >= warp_low)
-        attend_tile<HD, 8, true, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o, low_lo, low_hi,
-                                       ex.cap_log2, ex.cap_in);
+      if (warp_on && jbase <= warp_last && jbase + 63 >= warp_low) {
+        // a page that every row of the warp sees whole (behind no row's position, not before the last row's chunk, inside
+        // the window) needs no comparisons
+        if (jbase + 63 > warp_first || jbase < warp_low_last || (window > 0 && jbase <= warp_last - window))
+          attend_tile<HD, 8, true, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o, low_lo, low_hi,
+                                         ex.cap_log2, ex.cap_in);
+        else
+          attend_tile<HD, 8, false, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o, low_lo, low_hi,
+                                          ex.cap_log2, ex.cap_in);
+      }
     } else if (warp_on && jbase <= warp_last) {
       // visible to every row of this warp without a comparison: ends before the warp's first row's
       // position and starts after the window's lower edge of its last row

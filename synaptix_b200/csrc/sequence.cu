@@ -88,10 +88,25 @@ __global__ void __launch_bounds__(256) token_conv_kernel(const float* __restrict
   const int taps = P + 1;
   // row of y that holds the input at position p (start - P <= p <= pos)
   auto row_of = [&](int p) -> size_t { return p >= start ? (size_t)(t0 + (p - start)) : (size_t)(T + s * P + (p - start + P)); };
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float acc = y[(size_t)t * H + c];
-    for (int j = 0; j < taps; ++j) acc = fmaf(cw[(size_t)c * taps + j], y[row_of(pos - P + j) * H + c], acc);
-    out[(size_t)t * H + c] = from_f32<TO>(acc);
+  if ((H & 3) == 0) {                                        // four channels a thread, 16 bytes a load
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(y + (size_t)t * H + c);
+      for (int j = 0; j < taps; ++j) {
+        const float4 v = *reinterpret_cast<const float4*>(y + row_of(pos - P + j) * H + c);
+        a.x = fmaf(cw[(size_t)c * taps + j], v.x, a.x);
+        a.y = fmaf(cw[(size_t)(c + 1) * taps + j], v.y, a.y);
+        a.z = fmaf(cw[(size_t)(c + 2) * taps + j], v.z, a.z);
+        a.w = fmaf(cw[(size_t)(c + 3) * taps + j], v.w, a.w);
+      }
+      TO* o = out + (size_t)t * H + c;
+      o[0] = from_f32<TO>(a.x); o[1] = from_f32<TO>(a.y); o[2] = from_f32<TO>(a.z); o[3] = from_f32<TO>(a.w);
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float acc = y[(size_t)t * H + c];
+      for (int j = 0; j < taps; ++j) acc = fmaf(cw[(size_t)c * taps + j], y[row_of(pos - P + j) * H + c], acc);
+      out[(size_t)t * H + c] = from_f32<TO>(acc);
+    }
   }
   if (pos == end - 1) {
     float* hs = hist + (size_t)seq_slots[s] * P * H;
@@ -276,11 +291,20 @@ __global__ void __launch_bounds__(128) mingru_carry_kernel(float* __restrict__ A
   const int pieces = (n + MG_CH - 1) / MG_CH;
   float* sp = state + (size_t)seq_slots[s] * N + c;
   float S = *sp;
-  for (int p = 0; p < pieces; ++p) {
-    float* ab = AB + (((size_t)s * max_pieces + p) * 2) * N;
-    const float A = ab[c], B = ab[N + c];
-    ab[c] = S;
-    S = fmaf(A, S, B);
+  for (int p0 = 0; p0 < pieces; p0 += 8) {                 // eight pieces' (A, B) on the way at once, then the chain
+    float A[8], B[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float* ab = AB + (((size_t)s * max_pieces + min(p0 + k, pieces - 1)) * 2) * N;
+      A[k] = ab[c];
+      B[k] = ab[N + c];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (p0 + k < pieces) {
+        AB[(((size_t)s * max_pieces + p0 + k) * 2) * N + c] = S;
+        S = fmaf(A[k], S, B[k]);
+      }
   }
   *sp = S;
 }
@@ -307,6 +331,62 @@ __global__ void __launch_bounds__(128) mingru_apply_kernel(const T* __restrict__
   }
 }
 
+// The piece and apply kernels for projections whose rows and columns allow 16-byte loads: a block brings the 64 x 128
+// tile of each of its columns' arrays into shared memory with every thread's loads on the way at once, and a thread
+// then walks its channel there (a thread that fetches its own channel token by token has a few bytes in flight).
+#define MG_TC 128
+template <typename T, bool APPLY>
+__global__ void __launch_bounds__(MG_TC) mingru_tile_kernel(const T* __restrict__ proj, int row, int z_off, int x_off, int g_off,
+                                                            const float* __restrict__ bz, const float* __restrict__ bx,
+                                                            float* __restrict__ AB, T* __restrict__ out,
+                                                            const int* __restrict__ cu_seqlens, int N, int max_pieces) {
+  extern __shared__ __align__(16) unsigned char mg_smem[];
+  T* zs = reinterpret_cast<T*>(mg_smem);
+  T* xs = zs + MG_CH * MG_TC;
+  T* gs = xs + MG_CH * MG_TC;
+  pdl_wait();
+  pdl_trigger();
+  const int s = blockIdx.y, p = blockIdx.x, c0 = blockIdx.z * MG_TC, tid = threadIdx.x, c = c0 + tid;
+  const int t0 = cu_seqlens[s] + p * MG_CH, n = min(cu_seqlens[s + 1] - t0, MG_CH);
+  if (n <= 0) return;
+  constexpr int V = 16 / (int)sizeof(T), VPR = MG_TC / V;          // elements a load, loads a tile row
+  const int ncol = min(MG_TC, N - c0);                              // N is a multiple of V: a load is whole or absent
+  for (int idx = tid; idx < n * VPR; idx += MG_TC) {
+    const int j = idx / VPR, col = (idx % VPR) * V;
+    if (col >= ncol) continue;
+    const T* src = proj + (size_t)(t0 + j) * row + c0 + col;
+    *reinterpret_cast<uint4*>(zs + j * MG_TC + col) = *reinterpret_cast<const uint4*>(src + z_off);
+    *reinterpret_cast<uint4*>(xs + j * MG_TC + col) = *reinterpret_cast<const uint4*>(src + x_off);
+    if (APPLY) *reinterpret_cast<uint4*>(gs + j * MG_TC + col) = *reinterpret_cast<const uint4*>(src + g_off);
+  }
+  __syncthreads();
+  if (c >= N) return;
+  const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
+  float* ab = AB + (((size_t)s * max_pieces + p) * 2) * N;
+  if (!APPLY) {
+    float A = 1.f, B = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const float z = sigmoid_f32(to_f32(zs[j * MG_TC + tid]) + b_z);
+      const float u = to_f32(xs[j * MG_TC + tid]) + b_x;
+      const float keep = 1.f - z, add = z * (u >= 0.f ? u + 0.5f : sigmoid_f32(u));
+      A *= keep;
+      B = fmaf(keep, B, add);
+    }
+    ab[c] = A;
+    ab[N + c] = B;
+  } else {
+    float S = ab[c];
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const float z = sigmoid_f32(to_f32(zs[j * MG_TC + tid]) + b_z);
+      const float u = to_f32(xs[j * MG_TC + tid]) + b_x;
+      S = fmaf(1.f - z, S, z * (u >= 0.f ? u + 0.5f : sigmoid_f32(u)));
+      out[(size_t)(t0 + j) * N + c] = from_f32<T>(S * silu_f32(to_f32(gs[j * MG_TC + tid])));
+    }
+  }
+}
+
 template <typename T>
 static int mingru_launch(const void* proj, int row, int z_off, int x_off, int g_off, const float* bz, const float* bx,
                          float* state, void* out, float* scratch, const int* cu_seqlens, const int* seq_slots, int S, int N,
@@ -316,6 +396,24 @@ static int mingru_launch(const void* proj, int row, int z_off, int x_off, int g_
     return sx_launch(mingru_scan_kernel<T>, dim3(S, cb), dim3(128), 0, stream, (const T*)proj, row, z_off, x_off, g_off, bz, bx,
                      state, (T*)out, cu_seqlens, seq_slots, N);
   const int max_pieces = (max_new + MG_CH - 1) / MG_CH;
+  constexpr int V = 16 / (int)sizeof(T);
+  if (row % V == 0 && z_off % V == 0 && x_off % V == 0 && g_off % V == 0 && N % V == 0 && ((uintptr_t)proj & 15) == 0) {
+    const dim3 grid(max_pieces, S, (N + MG_TC - 1) / MG_TC);
+    const size_t tile = (size_t)MG_CH * MG_TC * sizeof(T);
+    if (3 * tile > 48 * 1024) {
+      cudaError_t ce = cudaFuncSetAttribute(mingru_tile_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(3 * tile));
+      if (ce != cudaSuccess) return (int)ce;
+      ce = cudaFuncSetAttribute(mingru_tile_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * tile));
+      if (ce != cudaSuccess) return (int)ce;
+    }
+    int e = sx_launch(mingru_tile_kernel<T, false>, grid, dim3(MG_TC), 2 * tile, stream, (const T*)proj, row, z_off, x_off, g_off, bz,
+                      bx, scratch, (T*)out, cu_seqlens, N, max_pieces);
+    if (e) return e;
+    e = sx_launch(mingru_carry_kernel, dim3(S, cb), dim3(128), 0, stream, scratch, state, cu_seqlens, seq_slots, N, max_pieces);
+    if (e) return e;
+    return sx_launch(mingru_tile_kernel<T, true>, grid, dim3(MG_TC), 3 * tile, stream, (const T*)proj, row, z_off, x_off, g_off, bz, bx,
+                     scratch, (T*)out, cu_seqlens, N, max_pieces);
+  }
   int e = sx_launch(mingru_piece_kernel<T>, dim3(max_pieces, S, cb), dim3(128), 0, stream, (const T*)proj, row, z_off, x_off, bz,
                     bx, scratch, cu_seqlens, N, max_pieces);
   if (e) return e;
@@ -581,11 +679,18 @@ __global__ void __launch_bounds__(256) retention_carry_kernel(float* __restrict_
   const float l2 = log2f(decay[hd]);
   float* sp = state + ((size_t)seq_slots[s] * heads + hd) * DE + i;
   float S = *sp;
-  for (int p = 0; p < pieces; ++p) {
-    float* u = U + (((size_t)s * max_pieces + p) * heads + hd) * DE + i;
-    const float add = *u;
-    *u = S;
-    S = fmaf(exp2f(l2 * (float)min(RC, n - p * RC)), S, add);
+  const float full = exp2f(l2 * (float)RC);
+  for (int p0 = 0; p0 < pieces; p0 += 8) {                 // eight pieces' sums on the way at once, then the chain
+    float add[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) add[k] = U[(((size_t)s * max_pieces + min(p0 + k, pieces - 1)) * heads + hd) * DE + i];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (p0 + k < pieces) {
+        const int p = p0 + k;
+        U[(((size_t)s * max_pieces + p) * heads + hd) * DE + i] = S;
+        S = fmaf(n - p * RC >= RC ? full : exp2f(l2 * (float)(n - p * RC)), S, add[k]);
+      }
   }
   *sp = S;
 }

@@ -86,11 +86,13 @@ def test_norm_and_short_convolution_over_portions(width, taps, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_mingru_recurrence_over_portions(dtype):
-    """Short portions (a thread walks the tokens) and long ones (pieces composed, then carried), the state going on."""
+@pytest.mark.parametrize("N", [70, 200])
+def test_mingru_recurrence_over_portions(dtype, N):
+    """Short portions (a thread walks the tokens) and long ones (pieces composed, then carried; with 200 channels through
+    tiles in shared memory, with 70 a thread fetching its own channel), the state going on."""
     from synaptix_b200 import ops
     g = torch.Generator().manual_seed(5)
-    N, K = 70, 24
+    K = 24
     W = {"p.z": torch.randn(N, K, generator=g) * 0.5, "p.x": torch.randn(N, K, generator=g), "p.g": torch.randn(N, K, generator=g),
          "p.z.b": torch.randn(N, generator=g), "p.x.b": torch.randn(N, generator=g), "p.o": torch.eye(N)}
     W = {k: v.double() for k, v in W.items()}
