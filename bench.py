@@ -231,10 +231,10 @@ VEMEDRA_SIZES = {
 
 def vemedra_config(width, ff, nh, nkv, hd, rh, runs, vocab):
     """``runs`` layer runs: layers (parallel, mingru, parallel, parallel) repeated, the first two run twice (a loop)."""
-    left = dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, softcap=50.0, mask=dict(size=1000),
-                rot=dict(dims=hd, base=250000.0))
+    left = dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, softcap=30.0, mask=dict(size=1000),
+                rot=dict(dims=hd, base=1.0e6))
     right = dict(heads=rh, dim=hd, vdim=hd // 2, decay=[1.0 - 2.0 ** -(3 + i % 8) for i in range(rh)])
-    par = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=0.6, right_scale=0.5),
+    par = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=0.75, right_scale=0.75),
                mlp=dict(kind="dense", ff=ff, limit=7.0))
     gru = dict(type="mingru", mixer=dict(width=width), mlp=None)
     n_layers = runs - 2

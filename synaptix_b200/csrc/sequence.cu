@@ -446,7 +446,7 @@ extern "C" int sx_mingru_piece_tokens() { return MG_CH; }
 // shared memory; thread (g, e) owns column e and the rows d = g, g + G, ... of S.
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) retention_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
+__global__ void __launch_bounds__(1024) retention_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
                                                         int g_off, const float* __restrict__ decay, float kscale, float eps,
                                                         int unit_norm, float out_scale, float* __restrict__ state,
                                                         T* __restrict__ out, int out_stride, const int* __restrict__ cu_seqlens,
@@ -508,8 +508,9 @@ extern "C" int sx_retention(const void* proj, int row, int q_off, int k_off, int
                             const int* cu_seqlens, const int* seq_slots, int S, int heads, int D, int E, int dt,
                             cudaStream_t stream) {
   if (S <= 0 || heads <= 0) return 0;
-  if (D <= 0 || E <= 0 || E > 256 || heads > 65535) return SX_ERR_SIZE;
-  const int G = 256 / E;
+  if (D <= 0 || E <= 0 || E > 1024 || heads > 65535) return SX_ERR_SIZE;
+  const int threads = E <= 256 ? 256 : (E <= 512 ? 512 : 1024);        // a thread a value element at least
+  const int G = threads / E;
   const size_t smem = ((size_t)D * E + 2 * D + E + (size_t)G * E) * sizeof(float);
   if (smem > 200 * 1024) return SX_ERR_SIZE;
   const dim3 grid(S, heads);
@@ -519,7 +520,7 @@ extern "C" int sx_retention(const void* proj, int row, int q_off, int k_off, int
       cudaError_t e = cudaFuncSetAttribute(retention_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                                                  \
     }                                                                                                                       \
-    return sx_launch(retention_kernel<TT>, grid, dim3(256), smem, stream, (const TT*)proj, row, q_off, k_off, v_off, g_off, \
+    return sx_launch(retention_kernel<TT>, grid, dim3(threads), smem, stream, (const TT*)proj, row, q_off, k_off, v_off, g_off, \
                      decay, kscale, eps, unit_norm, out_scale, state, (TT*)out, out_stride, cu_seqlens, seq_slots, heads, D, E); \
   }
   if (dt == SX_F32) RET_GO(float)
@@ -533,7 +534,7 @@ extern "C" int sx_retention(const void* proj, int row, int q_off, int k_off, int
 // global memory directly, every element once, without a stop in shared memory.
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) retention_step_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
+__global__ void __launch_bounds__(1024) retention_step_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
                                                              int g_off, const float* __restrict__ decay, float kscale, float eps,
                                                              int unit_norm, float out_scale, float* __restrict__ state,
                                                              T* __restrict__ out, int out_stride, const int* __restrict__ seq_slots,
@@ -809,7 +810,7 @@ extern "C" int sx_retention_any(const void* proj, int row, int q_off, int k_off,
                                 float* scratch, const int* cu_seqlens, const int* seq_slots, int S, int heads, int D, int E,
                                 int max_new, int mode, int dt, cudaStream_t stream) {
   if (S <= 0 || heads <= 0) return 0;
-  if (D <= 0 || E <= 0 || E > 256 || heads > 65535 || S > 65535) return SX_ERR_SIZE;
+  if (D <= 0 || E <= 0 || E > 1024 || heads > 65535 || S > 65535) return SX_ERR_SIZE;
   if (mode == 2) {
     if (!scratch || !sx_retention_pieces_fit(D, E)) return SX_ERR_SIZE;
     if (dt == SX_F32)
@@ -821,14 +822,15 @@ extern "C" int sx_retention_any(const void* proj, int row, int q_off, int k_off,
     return SX_ERR_DTYPE;
   }
   if (mode == 1) {
-    const int G = 256 / E;
+    const int threads = E <= 256 ? 256 : (E <= 512 ? 512 : 1024);
+    const int G = threads / E;
     const size_t smem = ((size_t)2 * D + (size_t)G * E) * sizeof(float);
     if (smem > 48 * 1024) return SX_ERR_SIZE;
     if (dt == SX_F32)
-      return sx_launch(retention_step_kernel<float>, dim3(S, heads), dim3(256), smem, stream, (const float*)proj, row, q_off, k_off,
+      return sx_launch(retention_step_kernel<float>, dim3(S, heads), dim3(threads), smem, stream, (const float*)proj, row, q_off, k_off,
                        v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, (float*)out, out_stride, seq_slots, heads, D, E);
     if (dt == SX_BF16)
-      return sx_launch(retention_step_kernel<bf16>, dim3(S, heads), dim3(256), smem, stream, (const bf16*)proj, row, q_off, k_off,
+      return sx_launch(retention_step_kernel<bf16>, dim3(S, heads), dim3(threads), smem, stream, (const bf16*)proj, row, q_off, k_off,
                        v_off, g_off, decay, kscale, eps, unit_norm, out_scale, state, (bf16*)out, out_stride, seq_slots, heads, D, E);
     return SX_ERR_DTYPE;
   }

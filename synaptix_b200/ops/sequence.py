@@ -104,7 +104,7 @@ def retention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, g_off: Opt
     # single tokens: the state goes through registers; long portions: pieces of 64 tokens (three kernels); else a block
     # a (sequence, head) walks the tokens
     mode, scratch, launches = 0, None, 1
-    if ctx.all_single and ctx.n_seqs == T and 2 * dim + 256 <= 12 * 1024:
+    if ctx.all_single and ctx.n_seqs == T and 2 * dim + max(256, 2 * vdim) <= 12 * 1024:
         mode = 1
     elif ctx.max_new >= PIECES_MIN_TOKENS and fn("sequence", "sx_retention_pieces_fit")(c_int(dim), c_int(vdim)):
         mode, launches = 2, 3

@@ -129,7 +129,7 @@ def test_mingru_recurrence_over_portions(dtype, N):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,D,E", [(3, 8, 12), (2, 64, 32), (1, 20, 100)])
+@pytest.mark.parametrize("heads,D,E", [(3, 8, 12), (2, 64, 32), (1, 20, 100), (1, 12, 300)])
 def test_retention_over_portions(heads, D, E, dtype):
     """A key far back must still count with a slow decay: token 3 of the long sequence has a key and a value ten times
     the others', and the last queries point at it."""
@@ -188,7 +188,7 @@ def test_retention_over_portions(heads, D, E, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,vd,chunk,cap", [(4, 2, 16, 8, 10, 30.0), (2, 2, 64, 64, 100, 30.0), (4, 2, 64, 64, 37, None),
-                                                      (3, 1, 32, 48, 64, 30.0), (2, 1, 128, 128, 70, 50.0), (6, 2, 32, 32, 120, 20.0)])
+                                                      (3, 1, 32, 48, 64, 30.0), (2, 1, 128, 128, 70, 40.0), (6, 2, 32, 32, 110, 20.0)])
 def test_attention_with_chunks_cap_and_sink(nh, nkv, hd, vd, chunk, cap, dtype):
     """Softmax attention over the paged cache with chunks of positions, capped scores, a sink per head and values of their
     own size, in a prompt portion and token by token.  Keys at the first and last place of a chunk, at page borders and far
@@ -418,3 +418,31 @@ def test_greedy_generation_through_the_entry_point(name):
         assert len(new) == 12
     out2 = llm.generate(prompts, max_new_tokens=12, temperature=0.0, prefill_batch=5)
     assert out2 == out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_replay_program_with_a_batch_whose_requests_end_at_different_times(tmp_path, dtype):
+    """``bin/trace_run`` as a user drives it (a subprocess fed JSON lines): three requests of unequal lengths begin in one
+    step, go on one token a step, the shorter ones end earlier, and a fourth runs afterwards in what they gave back."""
+    from test_gpu_trace_run import Replay
+    name = "VA"
+    V = vocab(name)
+    seqs = {f"q{i}": random_tokens(V, n, 800 + i) for i, n in enumerate([31, 75, 12, 50])}
+    refs = {k: oracle_logits(name, tuple(v)) for k, v in seqs.items()}
+    r = Replay(folder(name), dtype, str(tmp_path), 192)
+    heads = {"q0": 20, "q1": 60, "q2": 11}
+    got = r.step([{"id": k, "tokens": seqs[k][:h], "want": [0, h - 1]} for k, h in heads.items()])
+    assert_close(got, torch.stack([refs[k][j] for k, h in heads.items() for j in (0, h - 1)]), dtype, "replay: prompts")
+    at = dict(heads)
+    while at:
+        live = list(at)
+        ends = [k for k in live if at[k] + 1 == len(seqs[k])]
+        got = r.step([{"id": k, "tokens": [seqs[k][at[k]]], "want": [0]} for k in live], end=ends)
+        assert_close(got, torch.stack([refs[k][at[k]] for k in live]), dtype, f"replay: decode {sorted(at.values())}")
+        for k in live:
+            at[k] += 1
+            if k in ends:
+                del at[k]
+    got = r.step([{"id": "q3", "tokens": seqs["q3"], "want": [49]}], end=["q3"])
+    assert_close(got, refs["q3"][49:50], dtype, "replay: afterwards")
+    r.finish()

@@ -45,7 +45,7 @@ VB_INIT = dict(seed=7, std_matrix=0.09, std_embedding=0.5, std_gain=0.2, std_bia
 # a single tap (the convolution adds w * y of the token itself), no loop at all, head size 64 for keys and values
 # with two query heads a kv head (the sizes the fast bfloat16 attention kernels take), chunks of 100
 VF = dict(architecture="Vemedra", vocab=203, width=128, norm=dict(eps=1e-5), canon=dict(taps=1),
-          layers=[_par(_soft(4, 2, 64, 64, 0.125, 20.0, 100, 64, 2.5e5), dict(heads=2, dim=64, vdim=64, decay=[0.96875, 0.9990234375]), 0.6, 0.5, 256),
+          layers=[_par(_soft(4, 2, 64, 64, 0.125, 20.0, 100, 64, 4.0e5), dict(heads=2, dim=64, vdim=64, decay=[0.95, 0.998]), 0.8, 0.4, 256),
                   _gru(128),
                   _par(_soft(2, 2, 64, 64, 0.15, 50.0, 130, 32, 1.0e4), dict(heads=4, dim=32, vdim=32, decay=[0.9, 0.95, 0.99, 0.999]), 1.0, 1.0, 128)])
 VF_INIT = dict(seed=11, std_matrix=0.06, std_embedding=0.5, std_gain=0.1, std_bias=0.3)
