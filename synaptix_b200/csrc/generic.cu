@@ -475,7 +475,7 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_wide_kernel(
     const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
     const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq, float eps,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-    int maxp, int nh, int nkv, int n_pages) {
+    int maxp, int nh, int nkv, int n_pages, int row) {
   constexpr int HALF = HD / 2, LPH = HD / 16, HPW = 32 / LPH;      // lanes a head, heads a warp
   __shared__ float s_cs[HALF], s_sn[HALF], s_gq[HD], s_gk[HD];
   pdl_wait();
@@ -498,7 +498,7 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_wide_kernel(
   __syncthreads();
 
   const int n_heads = nh + 2 * nkv;
-  const bf16* src_tok = qkv + (size_t)t * n_heads * HD;
+  const bf16* src_tok = qkv + (size_t)t * row;                      // a row may hold other columns behind the heads
   const int sub = lane / LPH, e0 = (lane % LPH) * 8;               // which head of the warp's group; first value
   for (int hg = (blockIdx.y * QP_WARPS + warp) * HPW; hg < n_heads; hg += gridDim.y * QP_WARPS * HPW) {
     const int head = hg + sub;
@@ -569,12 +569,12 @@ static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, v
   const int pairs = inv_freq ? rotary_dim / 2 : 0;
   const bool packed = row == (nh + 2 * nkv) * hd && vd == hd;      // the layout the two faster kernels assume
   const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 7) == 0;
-  if (packed && sizeof(T) == 2 && (hd == 128 || hd == 64) && (!inv_freq || rotary_dim == hd) && grid.y == 1 &&
+  if (vd == hd && row % 8 == 0 && sizeof(T) == 2 && (hd == 128 || hd == 64) && (!inv_freq || rotary_dim == hd) && grid.y == 1 &&
       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0) {
 #define QP_WGO(HD)                                                                                                       \
   return sx_launch(qkv_prepare_wide_kernel<HD>, grid, dim3(QP_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out,      \
                    (bf16*)k_pages, (bf16*)v_pages, wq, wk, inv_freq, eps, positions, seq_of_token, block_table, maxp, nh,  \
-                   nkv, n_pages)
+                   nkv, n_pages, row)
     if (hd == 128) QP_WGO(128);
     QP_WGO(64);
 #undef QP_WGO

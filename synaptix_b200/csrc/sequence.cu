@@ -696,6 +696,30 @@ __global__ void __launch_bounds__(256) retention_carry_kernel(float* __restrict_
   *sp = S;
 }
 
+// Where the apply kernel's arrays lie in shared memory (in floats).  The keys' tile is dead once the scores are made, so the
+// piece's begin state takes its place; and where a thread has at most one tile of outputs (value heads of up to 64) they
+// wait in registers until the queries' tile is dead too and take its place: two blocks then fit an SM at 128 x 64 heads.
+struct RetLayout { int qt, ks, v, wt, o, pw, total, o_alias; };
+__host__ __device__ static inline RetLayout ret_layout(int D, int E) {
+  const int E4 = up4(E), LT = RC + 4;
+  RetLayout L;
+  L.qt = 0;
+  L.ks = D * LT;
+  L.v = L.ks + (D * LT > D * E4 ? D * LT : D * E4);
+  L.wt = L.v + RC * E4;
+  int end = L.wt + RC * LT;
+  L.o_alias = (E4 <= 64 && RC * E4 <= D * LT) ? 1 : 0;
+  if (L.o_alias) {
+    L.o = L.qt;
+  } else {
+    L.o = end;
+    end += RC * E4;
+  }
+  L.pw = end;
+  L.total = end + RC + 4;
+  return L;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) retention_apply_kernel(const T* __restrict__ proj, int row, int q_off, int k_off, int v_off,
                                                               int g_off, const float* __restrict__ decay, float kscale, float eps,
@@ -708,15 +732,16 @@ __global__ void __launch_bounds__(256) retention_apply_kernel(const T* __restric
   const int p = blockIdx.x, hd = blockIdx.y, s = blockIdx.z, tid = threadIdx.x;
   const int t0 = cu_seqlens[s] + p * RC, n = min(cu_seqlens[s + 1] - t0, RC);
   if (n <= 0) return;
-  const int D4 = up4(D), E4 = up4(E);
+  const int E4 = up4(E);
   constexpr int LT = RC + 4;          // leading size of the transposed arrays: their stores spread over banks
-  float* Qt = sm;                     // [D][LT]   Qt[d][i] = q_i[d]
-  float* Kt = Qt + (size_t)D * LT;    // [D][LT]   Kt[d][j] = k_j[d] * kscale
-  float* V = Kt + (size_t)D * LT;     // [RC][E4]
-  float* Sb = V + RC * E4;            // [D][E4]   the state at the piece's begin
-  float* Wt = Sb + (size_t)D * E4;    // [RC][LT]  Wt[j][i] = decay^(i-j) (q_i . k_j) for j <= i, else 0
-  float* O = Wt + RC * LT;            // [RC][E4]
-  float* pw = O + RC * E4;            // [RC + 1]  decay^n
+  const RetLayout L = ret_layout(D, E);
+  float* Qt = sm + L.qt;              // [D][LT]   Qt[d][i] = q_i[d]
+  float* Kt = sm + L.ks;              // [D][LT]   Kt[d][j] = k_j[d] * kscale; then
+  float* Sb = sm + L.ks;              // [D][E4]   the state at the piece's begin
+  float* V = sm + L.v;                // [RC][E4]
+  float* Wt = sm + L.wt;              // [RC][LT]  Wt[j][i] = decay^(i-j) (q_i . k_j) for j <= i, else 0
+  float* O = sm + L.o;                // [RC][E4]
+  float* pw = sm + L.pw;              // [RC + 1]  decay^n
   const float l2 = log2f(decay[hd]);
   for (int i = tid; i <= RC; i += 256) pw[i] = exp2f(l2 * (float)i);
   for (int i = tid; i < RC * D; i += 256) {
@@ -733,11 +758,6 @@ __global__ void __launch_bounds__(256) retention_apply_kernel(const T* __restric
     const int j = i / E4, e = i % E4;
     V[i] = (j < n && e < E) ? to_f32(proj[(size_t)(t0 + j) * row + v_off + hd * E + e]) : 0.f;
   }
-  const float* u = U + (((size_t)s * max_pieces + p) * heads + hd) * D * E;
-  for (int i = tid; i < D * E4; i += 256) {
-    const int d = i / E4, e = i % E4;
-    Sb[i] = e < E ? u[(size_t)d * E + e] : 0.f;
-  }
   __syncthreads();
   // Wt[j][i]: the product over d with m = j and n = i
   tile_product2(Kt, LT, Qt, LT, D, Kt, LT, Qt, LT, 0, RC, RC, [&](int m0, int n0, float (&a1)[4][4], float (&a2)[4][4]) {
@@ -750,13 +770,36 @@ __global__ void __launch_bounds__(256) retention_apply_kernel(const T* __restric
       }
   });
   __syncthreads();
+  const float* u = U + (((size_t)s * max_pieces + p) * heads + hd) * D * E;
+  for (int i = tid; i < D * E4; i += 256) {           // over the keys' tile
+    const int d = i / E4, e = i % E4;
+    Sb[i] = e < E ? u[(size_t)d * E + e] : 0.f;
+  }
+  __syncthreads();
   // O[i][e] = sum_j Wt[j][i] V[j][e] + decay^(i+1) sum_d Qt[d][i] Sb[d][e]
+  float held[4][4];
+  int held_m = -1, held_n = 0;
   tile_product2(Wt, LT, V, E4, n, Qt, LT, Sb, E4, D, RC, E4, [&](int m0, int n0, float (&a1)[4][4], float (&a2)[4][4]) {
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
-      for (int b = 0; b < 4; ++b) O[(m0 + a) * E4 + n0 + b] = fmaf(pw[m0 + a + 1], a2[a][b], a1[a][b]);
+      for (int b = 0; b < 4; ++b) {
+        const float x = fmaf(pw[m0 + a + 1], a2[a][b], a1[a][b]);
+        if (L.o_alias) held[a][b] = x;
+        else O[(m0 + a) * E4 + n0 + b] = x;
+      }
+    held_m = m0;
+    held_n = n0;
   });
+  if (L.o_alias) {                                     // the outputs take the queries' place once every thread is done with it
+    __syncthreads();
+    if (held_m >= 0) {
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) O[(held_m + a) * E4 + held_n + b] = held[a][b];
+    }
+  }
   __syncthreads();
   const int warp = tid >> 5, lane = tid & 31;
   for (int i = warp; i < n; i += 8) {
@@ -772,10 +815,7 @@ __global__ void __launch_bounds__(256) retention_apply_kernel(const T* __restric
   }
 }
 
-static size_t retention_apply_smem(int D, int E) {
-  const int E4 = up4(E), LT = RC + 4;
-  return ((size_t)2 * D * LT + (size_t)RC * E4 * 2 + (size_t)D * E4 + (size_t)RC * LT + RC + 4) * sizeof(float);
-}
+static size_t retention_apply_smem(int D, int E) { return (size_t)ret_layout(D, E).total * sizeof(float); }
 // can the long-portion form run for these sizes?  (its tiles have to fit an SM's shared memory)
 extern "C" int sx_retention_pieces_fit(int D, int E) { return retention_apply_smem(D, E) <= 200 * 1024 ? 1 : 0; }
 extern "C" int sx_retention_piece_tokens() { return RC; }
