@@ -446,3 +446,31 @@ def test_replay_program_with_a_batch_whose_requests_end_at_different_times(tmp_p
     got = r.step([{"id": "q3", "tokens": seqs["q3"], "want": [49]}], end=["q3"])
     assert_close(got, refs["q3"][49:50], dtype, "replay: afterwards")
     r.finish()
+
+
+def test_command_line_run_and_inspect(tmp_path):
+    """``python -m synaptix_b200 run`` chooses the model by config.json and generates greedily; ``inspect`` lists its layers."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "VB"
+    cfg, W = oracle(name)
+    prompt = random_tokens(vocab(name), 9, 1300)
+    env = dict(os.environ, PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "synaptix_b200", "run", folder(name), ",".join(map(str, prompt)),
+                        "--max-tokens", "6", "--temperature", "0", "--compute-dtype", "f32", "--stop-ids", "", "--json"],
+                       capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    seq = list(prompt)
+    for tok in out["outputs"][0]["tokens"]:
+        lg = PV.forward(cfg, W, seq)[-1]
+        top2 = lg.topk(2).values
+        if float(top2[0] - top2[1]) > 1e-3 * float(lg.abs().max()):
+            assert tok == int(lg.argmax())
+        seq.append(tok)
+    assert out["prompt_tokens"] == 9 and out["new_tokens"] == 6
+    r = subprocess.run([sys.executable, "-m", "synaptix_b200", "inspect", folder(name)], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and "architecture: Vemedra" in r.stdout and "layer 1: parallel, feed-forward 96" in r.stdout
