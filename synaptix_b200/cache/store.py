@@ -13,6 +13,8 @@ each group storage of its own:
   ``chunk`` says that a query sees only keys of its own chunk of that many
   positions (chunks counted from position 0): such a group gives a page back
   once every key in it lies before the chunk the sequence has reached.
+  ``keys_only`` says that the mixer reads its values out of the key rows (a
+  latent from which keys and values are both made): no storage for V.
 * ``StateRequest(shape, dtype)``: state of fixed size per sequence,
   ``[max_seqs + 1, *shape]`` per entry, zeroed when a slot is opened.  The last
   row belongs to no sequence (``Cache.spare_slot``): rows that pad a step up to
@@ -46,9 +48,12 @@ class KVRequest:
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
+    keys_only: bool = False
 
     @property
     def value_dim(self) -> int:
+        if self.keys_only:
+            return 0
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 

@@ -40,6 +40,10 @@ LIBRARIES: Dict[str, tuple] = {
     "generic": ("generic.cu", []),
     "sampling": ("sampling.cu", []),
     "sequence": ("sequence.cu", []),
+    "parallel": ("parallel.cu", []),
+    "mlstm": ("mlstm.cu", []),
+    "latent": ("latent.cu", []),
+    "moe": ("moe.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
     "attn_decode": ("attn_decode.cu", []),

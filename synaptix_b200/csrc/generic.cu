@@ -17,11 +17,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------
-// embedding gather: out[t, :] = float(table[ids[t], :]); an id outside the table gives zeros
+// embedding gather: out[t, :] = float(table[ids[t], :]) * scale; an id outside the table gives zeros
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int H, int V) {
+                                    float* __restrict__ out, int H, int V, float scale) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
@@ -29,16 +29,16 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   const bool ok = id >= 0 && id < V;
   const T* row = table + (size_t)(ok ? id : 0) * H;
   float* o = out + (size_t)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;
 }
 
 extern "C" int sx_embed_gather(const void* table, int dt, const int* ids, float* out,
-                               int n_tokens, int H, int V, cudaStream_t stream) {
+                               int n_tokens, int H, int V, float scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dt == SX_F32)
-    return sx_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)table, ids, out, H, V);
+    return sx_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)table, ids, out, H, V, scale);
   if (dt == SX_BF16)
-    return sx_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)table, ids, out, H, V);
+    return sx_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)table, ids, out, H, V, scale);
   return SX_ERR_DTYPE;
 }
 

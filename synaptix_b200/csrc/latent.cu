@@ -1,0 +1,308 @@
+// Attention over a cached latent (sm_100a), float32 and bfloat16.
+//
+// A token's cache row is [c | k_rot]: R = kv_rank elements of the normed latent and Dr rotated key elements that all
+// heads share; pages are [n_pages, 1, 64, R + Dr].  The keys and values of the heads are never formed: a query is
+// taken into the latent's space, attention weights are applied to c itself, and the value matrix of a head is applied
+// to the weighted latent.  Queries in the latent's space, scores, softmax and the weighted latents are 32-bit.
+//
+//   latent_prepare_kernel  one block a token, from the stacked input projection proj [T, row]:
+//                          cq = rmsnorm(proj[0:Rq]) * gq  -> cq_out [T, Rq]  (compute dtype)
+//                          c  = rmsnorm(proj[col:col+R]) * gkv, k_rot = rotate(proj[col+R : col+R+Dr])  -> the page row
+//                          (col < 0 or no pages: the layer reads another layer's cache and writes nothing)
+//   latent_query_kernel    one block a (tile of 8 tokens, head): q' = [Wuk_h^T q_h | rotate(q_rot_h)], float32
+//                          [T, H, R + Dr]; Wuk is [H * D, R], so q'[r] = sum_d q_h[d] Wuk[h D + d, r]
+//   latent_attn_kernel     one block a (token, group of 8 heads), a warp a head: key rows of the window staged in shared
+//                          memory 32 at a time for all heads of the block; a lane scores one key, the softmax runs
+//                          over the warp, and the weighted sum of c has a lane own the elements r = lane, lane + 32, ...
+//                          -> float32 [T, H, R]
+//   latent_output_kernel   one block a (tile of 8 tokens, head): y[h Dv + j] = sigmoid(gate_h) * sum_r Wuv[h Dv + j, r] o'[h, r]
+// Rotation: dims elements, pair i at angle position * inv_freq[i]; pairs = 1: elements (2i, 2i + 1), pairs = 0:
+// elements (i, i + dims / 2); elements from dims on pass unchanged.
+#include "common.cuh"
+#include <math.h>
+
+#define LT_THREADS 256
+#define LT_TOKENS 8          // tokens a block of the query / output kernels
+#define LT_HEADS 8           // heads (warps) a block of the attention kernel
+#define LT_KEYS 32           // keys staged at a time
+
+__device__ __forceinline__ void rot_pair_index(int i, int dims, int pairs, int& a, int& b) {
+  if (pairs) { a = 2 * i; b = 2 * i + 1; } else { a = i; b = i + dims / 2; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS) latent_prepare_kernel(
+    const T* __restrict__ proj, int row, int Rq, int col, int R, int Dr, const float* __restrict__ gq,
+    const float* __restrict__ gkv, float eps, const float* __restrict__ inv_freq, int dims, int pairs,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int maxp,
+    T* __restrict__ k_pages, T* __restrict__ cq_out) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const T* pr = proj + (size_t)t * row;
+  float ss = 0.f;
+  for (int i = tid; i < Rq; i += LT_THREADS) { const float v = to_f32(pr[i]); ss += v * v; }
+  ss = block_sum(ss, red);
+  float inv = rsqrtf(ss / (float)Rq + eps);
+  for (int i = tid; i < Rq; i += LT_THREADS) cq_out[(size_t)t * Rq + i] = from_f32<T>(to_f32(pr[i]) * inv * gq[i]);
+  if (col < 0 || k_pages == nullptr) return;
+  const int pos = positions[t];
+  const int page = block_table[(size_t)seq_of_token[t] * maxp + (pos >> 6)];
+  T* kr = k_pages + ((size_t)page * SX_PAGE + (pos & 63)) * (R + Dr);
+  ss = 0.f;
+  for (int i = tid; i < R; i += LT_THREADS) { const float v = to_f32(pr[col + i]); ss += v * v; }
+  ss = block_sum(ss, red);
+  inv = rsqrtf(ss / (float)R + eps);
+  for (int i = tid; i < R; i += LT_THREADS) kr[i] = from_f32<T>(to_f32(pr[col + i]) * inv * gkv[i]);
+  const T* rr = pr + col + R;
+  for (int i = tid; i < dims / 2; i += LT_THREADS) {
+    int ia, ib;
+    rot_pair_index(i, dims, pairs, ia, ib);
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    const float u = to_f32(rr[ia]), v = to_f32(rr[ib]);
+    kr[R + ia] = from_f32<T>(u * cs - v * sn);
+    kr[R + ib] = from_f32<T>(v * cs + u * sn);
+  }
+  for (int i = dims + tid; i < Dr; i += LT_THREADS) kr[R + i] = rr[i];
+}
+
+extern "C" int sx_latent_prepare(const void* proj, int row, int Rq, int col, int R, int Dr, const float* gq, const float* gkv,
+                                 float eps, const float* inv_freq, int dims, int pairs, const int* positions,
+                                 const int* seq_of_token, const int* block_table, int maxp, void* k_pages, void* cq_out,
+                                 int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (Rq <= 0 || dims < 0 || dims > Dr || (dims & 1) || (dims > 0 && inv_freq == nullptr)) return SX_ERR_SIZE;
+  if (dt == SX_F32)
+    return sx_launch(latent_prepare_kernel<float>, dim3(T), dim3(LT_THREADS), 0, stream, (const float*)proj, row, Rq, col, R, Dr,
+                     gq, gkv, eps, inv_freq, dims, pairs, positions, seq_of_token, block_table, maxp, (float*)k_pages, (float*)cq_out);
+  if (dt == SX_BF16)
+    return sx_launch(latent_prepare_kernel<bf16>, dim3(T), dim3(LT_THREADS), 0, stream, (const bf16*)proj, row, Rq, col, R, Dr,
+                     gq, gkv, eps, inv_freq, dims, pairs, positions, seq_of_token, block_table, maxp, (bf16*)k_pages, (bf16*)cq_out);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS) latent_query_kernel(
+    const T* __restrict__ q, const T* __restrict__ wuk, int H, int D, int Dr, int R, const float* __restrict__ inv_freq,
+    int dims, int pairs, const int* __restrict__ positions, float* __restrict__ qa, int n_tokens) {
+  extern __shared__ float qs[];          // LT_TOKENS * D
+  pdl_wait();
+  pdl_trigger();
+  const int t0 = blockIdx.x * LT_TOKENS, h = blockIdx.y, tid = threadIdx.x;
+  const int nt = min(LT_TOKENS, n_tokens - t0);
+  const int QW = H * (D + Dr);
+  for (int i = tid; i < LT_TOKENS * D; i += LT_THREADS) {
+    const int tt = i / D, d = i % D;
+    qs[i] = tt < nt ? to_f32(q[(size_t)(t0 + tt) * QW + h * (D + Dr) + d]) : 0.f;
+  }
+  __syncthreads();
+  for (int r = tid; r < R; r += LT_THREADS) {
+    float acc[LT_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = 0.f;
+    for (int d = 0; d < D; ++d) {
+      const float w = to_f32(wuk[((size_t)h * D + d) * R + r]);
+#pragma unroll
+      for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = fmaf(qs[tt * D + d], w, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < LT_TOKENS; ++tt)
+      if (tt < nt) qa[((size_t)(t0 + tt) * H + h) * (R + Dr) + r] = acc[tt];
+  }
+  // the rotated part
+  for (int i = tid; i < nt * (dims / 2); i += LT_THREADS) {
+    const int tt = i / (dims / 2), p = i % (dims / 2);
+    int ia, ib;
+    rot_pair_index(p, dims, pairs, ia, ib);
+    const T* qr = q + (size_t)(t0 + tt) * QW + h * (D + Dr) + D;
+    float sn, cs;
+    sincosf((float)positions[t0 + tt] * inv_freq[p], &sn, &cs);
+    const float u = to_f32(qr[ia]), v = to_f32(qr[ib]);
+    float* o = qa + ((size_t)(t0 + tt) * H + h) * (R + Dr) + R;
+    o[ia] = u * cs - v * sn;
+    o[ib] = v * cs + u * sn;
+  }
+  const int rest = Dr - dims;
+  for (int i = tid; i < nt * rest; i += LT_THREADS) {
+    const int tt = i / rest, j = dims + i % rest;
+    qa[((size_t)(t0 + tt) * H + h) * (R + Dr) + R + j] = to_f32(q[(size_t)(t0 + tt) * QW + h * (D + Dr) + D + j]);
+  }
+}
+
+extern "C" int sx_latent_query(const void* q, const void* wuk, int H, int D, int Dr, int R, const float* inv_freq, int dims,
+                               int pairs, const int* positions, float* qa, int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || H > 65535 || D < 0 || R <= 0 || dims < 0 || dims > Dr || (dims & 1)) return SX_ERR_SIZE;
+  const size_t smem = (size_t)LT_TOKENS * (D > 0 ? D : 1) * sizeof(float);
+  if (smem > 48 * 1024) return SX_ERR_SIZE;
+  dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H);
+  if (dt == SX_F32)
+    return sx_launch(latent_query_kernel<float>, grid, dim3(LT_THREADS), smem, stream, (const float*)q, (const float*)wuk, H, D, Dr,
+                     R, inv_freq, dims, pairs, positions, qa, T);
+  if (dt == SX_BF16)
+    return sx_launch(latent_query_kernel<bf16>, grid, dim3(LT_THREADS), smem, stream, (const bf16*)q, (const bf16*)wuk, H, D, Dr,
+                     R, inv_freq, dims, pairs, positions, qa, T);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// RI: elements of the weighted latent a lane owns (R <= 32 * RI)
+template <typename T, int RI>
+__global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
+    const float* __restrict__ qa, const T* __restrict__ k_pages, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int maxp, int H, int R, int Dr, float scale,
+    int window, float* __restrict__ out) {
+  extern __shared__ float sm[];
+  const int E = R + Dr, ES = E + 1;        // a staged row is padded by one float: lanes read different rows
+  float* ks = sm;                          // LT_KEYS * ES
+  float* qs = ks + LT_KEYS * ES;           // LT_HEADS * E
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y * LT_HEADS + warp;
+  const bool live = h < H;
+  const int pos = positions[t];
+  const int* bt = block_table + (size_t)seq_of_token[t] * maxp;
+  if (live)
+    for (int i = lane; i < E; i += 32) qs[warp * E + i] = qa[((size_t)t * H + h) * E + i];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  float m = -INFINITY, l = 0.f;
+  float acc[RI];
+#pragma unroll
+  for (int i = 0; i < RI; ++i) acc[i] = 0.f;
+  const float* qh = qs + warp * E;
+  for (int j0 = lo; j0 <= pos; j0 += LT_KEYS) {
+    const int nk = min(LT_KEYS, pos - j0 + 1);
+    __syncthreads();                        // the tile before is read out (and qs is written)
+    for (int i = tid; i < nk * E; i += LT_HEADS * 32) {
+      const int jj = i / E, e = i % E;
+      const int j = j0 + jj;
+      ks[jj * ES + e] = to_f32(k_pages[((size_t)bt[j >> 6] * SX_PAGE + (j & 63)) * E + e]);
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < nk) {
+      const float* kr = ks + lane * ES;
+      float d = 0.f;
+      for (int e = 0; e < E; ++e) d = fmaf(qh[e], kr[e], d);
+      s = d * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float p = lane < nk ? expf(s - m_new) : 0.f;
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < RI; ++i) acc[i] *= corr;
+    for (int jj = 0; jj < nk; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const float* kr = ks + jj * ES;
+#pragma unroll
+      for (int i = 0; i < RI; ++i) {
+        const int r = lane + 32 * i;
+        if (r < R) acc[i] = fmaf(pj, kr[r], acc[i]);
+      }
+    }
+  }
+  if (live) {
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < RI; ++i) {
+      const int r = lane + 32 * i;
+      if (r < R) out[((size_t)t * H + h) * R + r] = acc[i] * inv;
+    }
+  }
+}
+
+template <typename T, int RI>
+static int latent_attn_launch(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
+                              const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out,
+                              int T_, cudaStream_t stream) {
+  const size_t smem = (size_t)(LT_KEYS * (R + Dr + 1) + LT_HEADS * (R + Dr)) * sizeof(float);
+  if (smem > 200 * 1024) return SX_ERR_SIZE;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<T, RI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(T_, (H + LT_HEADS - 1) / LT_HEADS);
+  return sx_launch(latent_attn_kernel<T, RI>, grid, dim3(LT_HEADS * 32), smem, stream, qa, (const T*)k_pages, positions, seq_of_token,
+                   block_table, maxp, H, R, Dr, scale, window, out);
+}
+
+template <typename T>
+static int latent_attn_any(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
+                           const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out, int T_,
+                           cudaStream_t stream) {
+#define LT_CASE(RI) return latent_attn_launch<T, RI>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, T_, stream)
+  if (R <= 32 * 2) LT_CASE(2);
+  if (R <= 32 * 4) LT_CASE(4);
+  if (R <= 32 * 8) LT_CASE(8);
+  if (R <= 32 * 16) LT_CASE(16);
+  if (R <= 32 * 32) LT_CASE(32);
+#undef LT_CASE
+  return SX_ERR_SIZE;
+}
+
+extern "C" int sx_latent_attention(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
+                                   const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out,
+                                   int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || R <= 0 || Dr < 0 || (H + LT_HEADS - 1) / LT_HEADS > 65535) return SX_ERR_SIZE;
+  if (dt == SX_F32) return latent_attn_any<float>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, T, stream);
+  if (dt == SX_BF16) return latent_attn_any<bf16>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, T, stream);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS) latent_output_kernel(
+    const float* __restrict__ ol, const T* __restrict__ wuv, int H, int Dv, int R, const T* __restrict__ proj, int row,
+    int col_g, T* __restrict__ y, int n_tokens) {
+  extern __shared__ float os[];          // LT_TOKENS * R
+  pdl_wait();
+  pdl_trigger();
+  const int t0 = blockIdx.x * LT_TOKENS, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nt = min(LT_TOKENS, n_tokens - t0);
+  for (int i = tid; i < LT_TOKENS * R; i += LT_THREADS) {
+    const int tt = i / R, r = i % R;
+    os[i] = tt < nt ? ol[((size_t)(t0 + tt) * H + h) * R + r] : 0.f;
+  }
+  __syncthreads();
+  for (int j = warp; j < Dv; j += LT_THREADS / 32) {
+    float acc[LT_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = 0.f;
+    const T* wr = wuv + ((size_t)h * Dv + j) * R;
+    for (int r = lane; r < R; r += 32) {
+      const float w = to_f32(wr[r]);
+#pragma unroll
+      for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = fmaf(os[tt * R + r], w, acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < LT_TOKENS; ++tt) {
+      const float s = warp_sum(acc[tt]);
+      if (lane == 0 && tt < nt) {
+        float g = 1.f;
+        if (col_g >= 0) g = 1.f / (1.f + expf(-to_f32(proj[(size_t)(t0 + tt) * row + col_g + h])));
+        y[(size_t)(t0 + tt) * H * Dv + h * Dv + j] = from_f32<T>(s * g);
+      }
+    }
+  }
+}
+
+extern "C" int sx_latent_output(const float* ol, const void* wuv, int H, int Dv, int R, const void* proj, int row, int col_g,
+                                void* y, int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || H > 65535 || Dv <= 0 || R <= 0) return SX_ERR_SIZE;
+  const size_t smem = (size_t)LT_TOKENS * R * sizeof(float);
+  if (smem > 48 * 1024) return SX_ERR_SIZE;
+  dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H);
+  if (dt == SX_F32)
+    return sx_launch(latent_output_kernel<float>, grid, dim3(LT_THREADS), smem, stream, ol, (const float*)wuv, H, Dv, R,
+                     (const float*)proj, row, col_g, (float*)y, T);
+  if (dt == SX_BF16)
+    return sx_launch(latent_output_kernel<bf16>, grid, dim3(LT_THREADS), smem, stream, ol, (const bf16*)wuv, H, Dv, R,
+                     (const bf16*)proj, row, col_g, (bf16*)y, T);
+  return SX_ERR_DTYPE;
+}

@@ -23,12 +23,18 @@ from .options import OPTIONS, KernelOptions, options, set_options
 from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, embed_gather, gemm_generic, qkv_prepare,
                       residual_add, rope_table, silu_mul)
 from .sequence import add_rmsnorm_conv, capped_glu, mingru, retention, stream_add
+from .block import add_scaled, add_scaled_rmsnorm, scale_rows
+from .latent import latent_attention, latent_output, latent_prepare, latent_query
+from .mlstm import mlstm
+from .moe import ExpertPlan, moe_combine, moe_down, moe_gate_up, moe_route, moe_sort
 
 __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "decode_begin", "check_status", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
            "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table",
-           "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add", "gate_activation"]
+           "add_rmsnorm_conv", "capped_glu", "mingru", "retention", "stream_add", "gate_activation",
+           "add_scaled", "add_scaled_rmsnorm", "scale_rows", "latent_attention", "latent_output", "latent_prepare",
+           "latent_query", "mlstm", "ExpertPlan", "moe_combine", "moe_down", "moe_gate_up", "moe_route", "moe_sort"]
 
 
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),

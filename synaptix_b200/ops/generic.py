@@ -9,8 +9,9 @@ from ._lib import (KernelError, c_float, c_int, c_longlong, check, dt_code, fn, 
                    stream)
 
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out[t] = float32(table[ids[t]])``; ``ids`` int32 ``[T]``; result float32 ``[T, H]``."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 scale: float = 1.0) -> torch.Tensor:
+    """``out[t] = float32(table[ids[t]]) * scale``; ``ids`` int32 ``[T]``; result float32 ``[T, H]``."""
     require_cuda(table, ids, out)
     V, H = table.shape
     T = ids.numel()
@@ -19,7 +20,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Ten
     if out is None:
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     check(fn("generic", "sx_embed_gather")(ptr(table), c_int(dt_code(table.dtype)), ptr(ids), ptr(out),
-                                           c_int(T), c_int(H), c_int(V), stream()), "embed_gather")
+                                           c_int(T), c_int(H), c_int(V), c_float(scale), stream()), "embed_gather")
     return out
 
 

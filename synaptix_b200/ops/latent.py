@@ -1,0 +1,86 @@
+"""Python faces of the kernels in ``csrc/latent.cu``: attention over a cached latent.  A token's cache row is
+``[c | k_rot]`` (``kv_rank`` + ``rot_dim`` elements, one head); queries in the latent's space and weighted latents are
+float32."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._lib import KernelError, c_float, c_int, check, dt_code, fn, ptr, require_cuda, stream
+
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, col_kv: int, kv_rank: int, rot_dim: int, gain_q: torch.Tensor,
+                   gain_kv: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int, pairs: bool,
+                   ctx, block_table: torch.Tensor, k_pages: Optional[torch.Tensor]) -> torch.Tensor:
+    """From the stacked input projection ``proj [T, row]``: the normed query latent ``rmsnorm(proj[:, :q_rank]) * gain_q``
+    (returned, ``proj``'s dtype) and, if ``k_pages`` is given, the token's cache row: ``rmsnorm(proj[:, col_kv : col_kv +
+    kv_rank]) * gain_kv`` and behind it the next ``rot_dim`` columns with their first ``rot_dims`` elements rotated
+    (``pairs``: neighbouring elements paired, else element ``i`` with ``i + rot_dims / 2``)."""
+    require_cuda(proj, gain_q, gain_kv, inv_freq, block_table, k_pages)
+    T, row = proj.shape
+    if k_pages is not None:
+        if col_kv < 0 or col_kv + kv_rank + rot_dim > row or gain_kv is None:
+            raise KernelError("latent_prepare: the key/value latent's columns do not fit")
+        if k_pages.dtype != proj.dtype or k_pages.dim() != 4 or tuple(k_pages.shape[1:]) != (1, 64, kv_rank + rot_dim):
+            raise KernelError("latent_prepare: cache pages must be [n_pages, 1, 64, kv_rank + rot_dim] of the compute dtype")
+    if q_rank > row or gain_q.numel() != q_rank:
+        raise KernelError("latent_prepare: the query latent does not fit")
+    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    check(fn("latent", "sx_latent_prepare")(
+        ptr(proj), c_int(row), c_int(q_rank), c_int(col_kv if k_pages is not None else -1), c_int(kv_rank), c_int(rot_dim),
+        ptr(gain_q), ptr(gain_kv), c_float(eps), ptr(inv_freq), c_int(rot_dims if inv_freq is not None else 0),
+        c_int(1 if pairs else 0), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table), c_int(block_table.shape[1]),
+        ptr(k_pages), ptr(cq), c_int(T), c_int(dt_code(proj.dtype)), stream()), "latent_prepare")
+    return cq
+
+
+def latent_query(q: torch.Tensor, wuk: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int,
+                 inv_freq: Optional[torch.Tensor], rot_dims: int, pairs: bool, ctx) -> torch.Tensor:
+    """Queries ``q [T, heads * (dim + rot_dim)]`` taken into the latent's space: per head
+    ``[Wuk_h^T q_h | rotate(q_rot_h)]`` with ``wuk [heads * dim, kv_rank]``; float32 ``[T, heads, kv_rank + rot_dim]``."""
+    require_cuda(q, wuk, inv_freq)
+    T = q.shape[0]
+    if q.shape[1] != heads * (dim + rot_dim) or tuple(wuk.shape) != (heads * dim, kv_rank) or wuk.dtype != q.dtype:
+        raise KernelError("latent_query: sizes do not fit")
+    qa = torch.empty((T, heads, kv_rank + rot_dim), dtype=torch.float32, device=q.device)
+    check(fn("latent", "sx_latent_query")(ptr(q), ptr(wuk), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank),
+                                          ptr(inv_freq), c_int(rot_dims if inv_freq is not None else 0),
+                                          c_int(1 if pairs else 0), ptr(ctx.positions), ptr(qa), c_int(T),
+                                          c_int(dt_code(q.dtype)), stream()), "latent_query")
+    return qa
+
+
+def latent_attention(qa: torch.Tensor, k_pages: torch.Tensor, ctx, block_table: torch.Tensor, heads: int, kv_rank: int,
+                     rot_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
+    """Causal (optionally windowed) softmax attention of ``qa`` float32 ``[T, heads, kv_rank + rot_dim]`` over the cache
+    rows ``[c | k_rot]``; the weights are applied to ``c``: float32 ``[T, heads, kv_rank]``."""
+    require_cuda(qa, k_pages, block_table)
+    T = qa.shape[0]
+    if qa.dtype != torch.float32 or tuple(qa.shape[1:]) != (heads, kv_rank + rot_dim):
+        raise KernelError("latent_attention: queries are float32 [T, heads, kv_rank + rot_dim]")
+    if k_pages.dim() != 4 or tuple(k_pages.shape[1:]) != (1, 64, kv_rank + rot_dim):
+        raise KernelError("latent_attention: cache pages must be [n_pages, 1, 64, kv_rank + rot_dim]")
+    out = torch.empty((T, heads, kv_rank), dtype=torch.float32, device=qa.device)
+    check(fn("latent", "sx_latent_attention")(ptr(qa), ptr(k_pages), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
+                                              c_int(block_table.shape[1]), c_int(heads), c_int(kv_rank), c_int(rot_dim),
+                                              c_float(scale), c_int(0 if window is None else int(window)), ptr(out), c_int(T),
+                                              c_int(dt_code(k_pages.dtype)), stream()), "latent_attention")
+    return out
+
+
+def latent_output(ol: torch.Tensor, wuv: torch.Tensor, heads: int, vdim: int, kv_rank: int, proj: torch.Tensor, col_gate: int,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """``y[t, h * vdim + j] = sigmoid(proj[t, col_gate + h]) * sum_r wuv[h * vdim + j, r] * ol[t, h, r]`` (no gate if
+    ``col_gate < 0``); ``[T, heads * vdim]`` in ``out_dtype``."""
+    require_cuda(ol, wuv, proj)
+    T = ol.shape[0]
+    if ol.dtype != torch.float32 or tuple(ol.shape[1:]) != (heads, kv_rank) or tuple(wuv.shape) != (heads * vdim, kv_rank):
+        raise KernelError("latent_output: sizes do not fit")
+    if wuv.dtype != out_dtype or proj.dtype != out_dtype or (col_gate >= 0 and col_gate + heads > proj.shape[1]):
+        raise KernelError("latent_output: dtypes or the gate's columns do not fit")
+    y = torch.empty((T, heads * vdim), dtype=out_dtype, device=ol.device)
+    check(fn("latent", "sx_latent_output")(ptr(ol), ptr(wuv), c_int(heads), c_int(vdim), c_int(kv_rank), ptr(proj),
+                                           c_int(proj.shape[1]), c_int(col_gate), ptr(y), c_int(T), c_int(dt_code(out_dtype)),
+                                           stream()), "latent_output")
+    return y

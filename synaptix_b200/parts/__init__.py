@@ -1,16 +1,17 @@
 from .attention import Attention
 from .base import (FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, PositionEncoding, Runtime, ScaledRows,
                    StepContext)
-from .block import ConvPreNormBlock, PreNormBlock, TokenConv
+from .block import ConvPreNormBlock, ParallelBlock, PreNormBlock, TokenConv
 from .embedding import Embedding, OutputHead
 from .linear import JoinedLinear, Linear
-from .mlp import CappedGLU, SwiGLU
+from .latent import LatentAttention
+from .mlp import CappedGLU, MixtureOfExperts, SwiGLU
 from .norm import RMSNorm
 from .parallel import ParallelMixers
-from .recurrent import MinGRU, Retention
-from .rope import NoPosition, RotaryHalf, rotary_inv_freq
+from .recurrent import MLSTM, MinGRU, Retention
+from .rope import NoPosition, RotaryHalf, RotaryPairs, rotary_inv_freq
 
 __all__ = ["Attention", "FeedForward", "Mixer", "Norm", "Part", "PendingLinear", "PendingNorm", "ScaledRows", "PositionEncoding", "Runtime",
            "StepContext", "PreNormBlock", "ConvPreNormBlock", "TokenConv", "Embedding", "OutputHead", "Linear", "JoinedLinear",
            "SwiGLU", "CappedGLU", "RMSNorm", "ParallelMixers", "MinGRU", "Retention", "NoPosition", "RotaryHalf",
-           "rotary_inv_freq"]
+           "rotary_inv_freq", "ParallelBlock", "LatentAttention", "MixtureOfExperts", "MLSTM", "RotaryPairs"]

@@ -146,7 +146,34 @@ class PendingLinear:
 
 def plain(t):
     """``t`` as a tensor, whatever deferred form it came in."""
-    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows)) else t
+    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows, ScaledSum)) else t
+
+
+class ScaledSum:
+    """Branches of a layer that have not been added into the residual stream yet: ``sum_i scale_i * x_i`` with
+    ``x_i [T, width]`` (compute dtype or float32) and ``scale_i`` a float32 vector over the width (or ``None`` for
+    ones).  A block whose branches read the same stream hands this on, so that the next norm's kernel forms the sum,
+    adds it into the stream and normalises in one pass (``Norm.add_forward`` of a norm that says ``takes_scaled_sum``).
+    ``materialize()`` gives the sum as one float32 tensor (a kernel of its own)."""
+    __slots__ = ("terms", "_sum")
+
+    def __init__(self, terms):
+        self.terms = [(x, s) for x, s in terms]
+        if not 1 <= len(self.terms) <= 2:
+            raise ValueError("a scaled sum has one or two terms")
+        self._sum = None
+
+    @property
+    def shape(self):
+        return self.terms[0][0].shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._sum is None:
+            from .. import ops
+            x0 = self.terms[0][0]
+            self._sum = torch.zeros(x0.shape, dtype=torch.float32, device=x0.device)
+            ops.add_scaled(self._sum, self.terms)
+        return self._sum
 
 
 class ScaledRows:
@@ -209,6 +236,7 @@ class Part:
 
 class Norm(Part):
     takes_pending_product = False  # True: add_forward may be handed a PendingLinear as delta
+    takes_scaled_sum = False       # True: add_forward may be handed a ScaledSum as delta
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

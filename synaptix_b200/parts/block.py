@@ -10,6 +10,12 @@ between each norm and its sublayer: what a sublayer reads is ``y + conv(y)`` wit
 ``y = norm(h)``, ``conv(y)_t = sum_j w[:, j] * y_(t - taps + 1 + j)`` per channel, zeros
 before the sequence's start (``TokenConv``).  The last ``taps - 1`` inputs of each
 convolution are part of a sequence's state; the feed-forward half may be absent.
+
+``ParallelBlock``: mixer and feed-forward side by side on the SAME stream, each behind a
+norm of its own and times a learned vector over the width (a layer scale):
+``h += mult * (ls1 * mixer(norm1(h)) + ls2 * ffn(norm2(h)))``.  Both norms share the
+row's root mean square, so one kernel makes both; the sum is handed on as a
+``ScaledSum`` and added by the next norm's kernel.  The feed-forward half may be absent.
 """
 from __future__ import annotations
 
@@ -20,8 +26,8 @@ import torch
 from .. import ops
 from ..cache.store import BundleRequest, StateRequest
 from ..weights.loader import TensorSpec
-from .base import (FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, StepContext, plain,
-                   to_device_f32)
+from .base import (FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum,
+                   StepContext, plain, to_device_f32)
 
 
 class PreNormBlock(Part):
@@ -106,3 +112,55 @@ class ConvPreNormBlock(Part):
             return h, a
         y = ops.add_rmsnorm_conv(h, plain(a), self.norm2.weight, self.norm2.eps, self.conv2.weight, views[2], ctx, dtype)
         return h, self.ffn.forward(y, ctx)
+
+
+class ParallelBlock(Part):
+    """``h += mult * (ls1 * mixer(norm1(h)) + ls2 * ffn(norm2(h)))``, both branches of the same ``h``.  ``norm1`` and
+    ``norm2`` are RMS norms (their gains may differ, their eps not); ``scale_names`` are the tensors ``ls1`` and
+    ``ls2`` (vectors over the width).  ``norm2`` and ``ffn`` may both be ``None``."""
+    takes_pending_product = False
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], *,
+                 scale_names: Tuple[str, str], mult: float = 1.0):
+        if (norm2 is None) != (ffn is None):
+            raise ValueError("norm2 and ffn come together or not at all")
+        if norm2 is not None and norm2.eps != norm1.eps:
+            raise ValueError("the two norms of a parallel block share their eps")
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self.scale_names = tuple(scale_names)
+        self.mult = float(mult)
+        self.width = norm1.width
+        self.s1: Optional[torch.Tensor] = None
+        self.s2: Optional[torch.Tensor] = None
+
+    def children(self) -> List[Part]:
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs = {self.scale_names[0]: TensorSpec((self.width,), "gain")}
+        if self.ffn is not None:
+            specs[self.scale_names[1]] = TensorSpec((self.width,), "gain")
+        return specs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        # mult * (ls1 * a + ls2 * b) as (mult ls1) * a + (mult ls2) * b, the factors formed once in 32-bit
+        self.s1 = to_device_f32(tensors[self.scale_names[0]].to(torch.float32) * self.mult, rt)
+        if self.ffn is not None:
+            self.s2 = to_device_f32(tensors[self.scale_names[1]].to(torch.float32) * self.mult, rt)
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, cache_view, write_cache: bool = True):
+        if isinstance(pending, ScaledSum):
+            terms = pending.terms
+        else:
+            pending = plain(pending)
+            terms = [] if pending is None else [(pending, None)]
+        gains = [self.norm1.weight] + ([self.norm2.weight] if self.ffn is not None else [])
+        xs = ops.add_scaled_rmsnorm(h, terms, gains, self.norm1.eps, ctx.runtime.dtype)
+        a = self.mixer.forward(xs[0], ctx, cache_view, write_cache)
+        if self.ffn is None:
+            return h, ScaledSum([(a, self.s1)])
+        b = self.ffn.forward(xs[1], ctx)
+        return h, ScaledSum([(a, self.s1), (b, self.s2)])

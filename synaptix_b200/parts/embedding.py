@@ -18,8 +18,11 @@ from .linear import Linear
 
 
 class Embedding(Part):
-    def __init__(self, weight_name: str, vocab: int, width: int):
+    """``scale``: the gathered rows are multiplied by it (in 32-bit, on their way into the stream)."""
+
+    def __init__(self, weight_name: str, vocab: int, width: int, scale: float = 1.0):
         self.weight_name, self.vocab, self.width = weight_name, vocab, width
+        self.scale = float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -30,14 +33,17 @@ class Embedding(Part):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         """float32 residual stream ``[T, width]``."""
-        return ops.embed_gather(self.weight, token_ids)
+        return ops.embed_gather(self.weight, token_ids, scale=self.scale)
 
 
 class OutputHead(Part):
-    """``tied`` is True, False, or None (= tied iff the weights hold no matrix of that name)."""
+    """``tied`` is True, False, or None (= tied iff the weights hold no matrix of that name).  ``scale``: the logits
+    are multiplied by it (in 32-bit)."""
 
-    def __init__(self, weight_name: str, vocab: int, width: int, tied: Optional[bool], embedding: Embedding):
+    def __init__(self, weight_name: str, vocab: int, width: int, tied: Optional[bool], embedding: Embedding,
+                 scale: float = 1.0):
         self.weight_name, self.vocab, self.width = weight_name, vocab, width
+        self.scale = float(scale)
         self.tied = tied
         self.embedding = embedding
         self.linear = Linear(weight_name, width, vocab)
@@ -56,4 +62,7 @@ class OutputHead(Part):
 
     def forward(self, x) -> torch.Tensor:
         """``x``: the normalised rows, or a ``PendingNorm`` of them."""
-        return self.linear.forward(x, out_dtype=torch.float32)
+        logits = self.linear.forward(x, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ops.scale_rows(logits, self.scale)
+        return logits

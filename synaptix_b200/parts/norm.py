@@ -1,4 +1,4 @@
-"""RMSNorm with a plain gain, fused with the residual sum.
+"""RMSNorm with a plain gain (or a gain stored around zero: ``offset + w``), fused with the residual sum.
 
 Formula (crates/synaptix-ops/src/norm/rms_norm.rs:17-26; CUDA
 crates/synaptix-kernels-cuda/src/cu/reduction/rms_norm.cu:84-96):
@@ -14,30 +14,39 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, PendingLinear, PendingNorm, Runtime, ScaledRows, to_device_f32
+from .base import Norm, PendingLinear, PendingNorm, Runtime, ScaledRows, ScaledSum, to_device_f32
 
 
 class RMSNorm(Norm):
-    def __init__(self, weight_name: str, width: int, eps: float):
+    """``offset``: the stored tensor ``w`` lies around zero and the gain is ``offset + w`` (formed once, in 32-bit,
+    when the weights are bound); 0 is the plain gain."""
+
+    def __init__(self, weight_name: str, width: int, eps: float, offset: float = 0.0):
         self.weight_name = weight_name
         self.width = width
         self.eps = float(eps)
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
         self._dtype = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.weight_name: TensorSpec((self.width,), "gain")}
+        return {self.weight_name: TensorSpec((self.width,), "gain" if self.offset == 0.0 else "gain0")}
 
     def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
-        self.weight = to_device_f32(tensors[self.weight_name], rt)
+        w = tensors[self.weight_name].to(torch.float32)
+        self.weight = to_device_f32(w + self.offset if self.offset != 0.0 else w, rt)
         self._dtype = rt.dtype
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(h, None, self.weight, self.eps, self._dtype)
 
     takes_pending_product = True
+    takes_scaled_sum = True
 
     def add_forward(self, h, delta, rows=None, lazy=False):
+        if isinstance(delta, ScaledSum):
+            # the branches' sum, the sum into the stream and the norm in one kernel
+            return ops.add_scaled_rmsnorm(h, delta.terms, [self.weight], self.eps, self._dtype, rows=rows)[0]
         if isinstance(delta, PendingLinear):
             N, K = delta.weight.shape
             if (lazy and rows is None and N == self.width and h.dtype == torch.float32 and h.is_contiguous()

@@ -12,7 +12,15 @@ projections of the input (``n`` channels each; the first two with a bias):
     S_t = decay S_(t-1) + (k_t k_scale) v_t^T,   o_t = S_t^T q_t,
     out = Wo (o_t / rms(o_t) * silu(a_g))        (unit norm and gate optional)
 
-Both states start at zero, live in 32-bit in the cache's per-sequence state storage and go on from step to step; the
+``MLSTM``: a matrix memory per head with exponential gates and a running maximum that keeps them in range.  Per head,
+with ``q`` (times ``dim^-1/2``) and ``k`` of ``dim`` and ``v`` of ``vdim`` elements, log gates
+``i = cap tanh((Wi x + bi) / cap)`` and ``f = logsigmoid(cap tanh((Wf x + bf) / cap))``:
+
+    m_t = max(f + m_(t-1), i),           S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T,
+    n_t = the same with k alone,         o_t = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6),
+    out = Wo (o_t / rms(o_t) * gain * sigmoid(Wg x))        (S, n and m start at 0)
+
+All states start at zero, live in 32-bit in the cache's per-sequence state storage and go on from step to step; the
 gates, decays, norms and sums are 32-bit whatever the compute dtype.  Both parts can run alone (they own their
 projections) or ``shared``: beside other mixers under one owner that stacks the projections of all of them
 (``input_parts``, ``output_part``, ``mix``).
@@ -24,7 +32,7 @@ from typing import Dict, List, Mapping, Optional, Sequence
 import torch
 
 from .. import ops
-from ..cache.store import StateRequest
+from ..cache.store import BundleRequest, StateRequest
 from ..weights.loader import TensorSpec
 from .base import Mixer, Part, Runtime, StepContext, to_device_f32
 from .linear import Linear
@@ -123,3 +131,55 @@ class Retention(Mixer):
                 defer_output: bool = False):
         y = self.mix(self.proj.forward(x), 0, ctx, state, write_cache)
         return self.o.deferred(y) if defer_output else self.o.forward(y)
+
+
+class MLSTM(Mixer):
+    accepts_lazy_input = False
+    can_defer_output = False
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "i": "i", "f": "f", "i_bias": "i.b", "f_bias": "f.b",
+             "norm": "norm"}
+    DENOMINATOR_EPS = 1e-6          # added to the denominator max(|n . q|, exp(-m))
+
+    def __init__(self, prefix: str, width: int, heads: int, dim: int, vdim: int, *, gate_cap: float,
+                 unit_norm_eps: float, q_scale: Optional[float] = None, names: Optional[Mapping[str, str]] = None):
+        self.prefix, self.width = prefix, width
+        self.heads, self.dim, self.vdim = heads, dim, vdim
+        self.gate_cap = float(gate_cap)
+        self.unit_norm_eps = float(unit_norm_eps)
+        self.q_scale = float(q_scale) if q_scale is not None else float(dim) ** -0.5
+        self.names = n = dict(self.NAMES, **(names or {}))
+        p = prefix
+        self.proj = Linear([p + n["q"], p + n["k"], p + n["v"], p + n["g"]], width,
+                           [heads * dim, heads * dim, heads * vdim, heads * vdim])
+        # the gates' pre-activations leave their product in 32-bit: they are summed over the whole sequence
+        self.gates = Linear([p + n["i"], p + n["f"]], width, [heads, heads])
+        self.o = Linear(p + n["o"], heads * vdim, width)
+        self.bias: Optional[torch.Tensor] = None
+        self.norm_gain: Optional[torch.Tensor] = None
+
+    def children(self) -> List[Part]:
+        return [self.proj, self.gates, self.o]
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        p, n = self.prefix, self.names
+        return {p + n["i_bias"]: TensorSpec((self.heads,), "bias"), p + n["f_bias"]: TensorSpec((self.heads,), "bias"),
+                p + n["norm"]: TensorSpec((self.heads * self.vdim,), "gain")}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        p, n = self.prefix, self.names
+        self.bias = to_device_f32(torch.cat([tensors[p + n["i_bias"]].float(), tensors[p + n["f_bias"]].float()]), rt)
+        self.norm_gain = to_device_f32(tensors[p + n["norm"]], rt)
+
+    def cache_request(self):
+        return BundleRequest((StateRequest((self.heads, self.dim, self.vdim), torch.float32),
+                              StateRequest((self.heads, self.dim), torch.float32),
+                              StateRequest((self.heads,), torch.float32)))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, state, write_cache: bool = True):
+        a = self.proj.forward(x)
+        g = self.gates.forward(x, out_dtype=torch.float32)
+        hq, hv = self.heads * self.dim, self.heads * self.vdim
+        y = ops.mlstm(a, 0, hq, 2 * hq, 2 * hq + hv, g, self.bias, self.gate_cap, self.q_scale, self.heads, self.dim,
+                      self.vdim, self.norm_gain, self.unit_norm_eps, self.DENOMINATOR_EPS, state[0], state[1], state[2], ctx)
+        return self.o.forward(y)

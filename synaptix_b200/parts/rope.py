@@ -32,6 +32,8 @@ _INV_FREQ = {}
 
 
 class RotaryHalf(PositionEncoding):
+    pairs = False
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int = None):
         self.head_dim = head_dim
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
@@ -48,6 +50,22 @@ class RotaryHalf(PositionEncoding):
 
     def rotation(self):
         return self.inv_freq, self.rotary_dim
+
+
+class RotaryPairs(RotaryHalf):
+    """The same angles with NEIGHBOURING elements paired: element ``2i`` with ``2i + 1`` (the interleaved layout),
+    ``(u, v) -> (u cos - v sin, v cos + u sin)`` at angle ``position * theta^(-2i / rotary_dim)``.  Kernels that
+    rotate ask ``pairs``: ``True`` here, ``False`` for the rotate-half layout."""
+    pairs = True
+
+    def bind(self, tensors, rt: Runtime) -> None:
+        # frequencies to the nearest 32-bit value (formed in 64-bit, rounded once)
+        key = ("pairs", self.theta, self.rotary_dim, str(rt.device))
+        if key not in _INV_FREQ:
+            i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+            f = np.power(np.float64(self.theta), -2.0 * i / self.rotary_dim).astype(np.float32)
+            _INV_FREQ[key] = torch.from_numpy(f).to(rt.device)
+        self.inv_freq = _INV_FREQ[key]
 
 
 class NoPosition(PositionEncoding):

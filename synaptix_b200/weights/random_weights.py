@@ -39,7 +39,7 @@ class RandomSource(WeightSource):
     """Seeded normal weights for a set of tensor specs.
 
     ``matrix`` ~ N(0, std_matrix), ``embedding`` ~ N(0, std_embedding),
-    ``gain`` ~ 1 + N(0, std_gain), ``bias`` ~ N(0, std_bias) (biases, taps of short convolutions, sinks),
+    ``gain`` ~ 1 + N(0, std_gain), ``gain0`` ~ N(0, std_gain) (a gain stored around zero), ``bias`` ~ N(0, std_bias) (biases, taps of short convolutions, sinks),
     ``table`` = zeros (int32).  Floating tensors
     are drawn in float32 and stored as ``dtype`` (``gain_dtype`` for gains).
     """
@@ -71,6 +71,8 @@ class RandomSource(WeightSource):
         x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=self.device)
         if spec.kind == "gain":
             return (1.0 + self.std_gain * x).to(self.gain_dtype)
+        if spec.kind == "gain0":
+            return (self.std_gain * x).to(self.gain_dtype)
         if spec.kind == "bias":
             return (self.std_bias * x).to(self.dtype)
         if spec.kind == "embedding":
