@@ -182,7 +182,12 @@ def cmd_inspect(a) -> int:
                     print(f"  {k}: " + ", ".join(f"{kk} {vv}" for kk, vv in v.items()))
             for i, layer in enumerate(d["layers"]):
                 ff = layer.get("mlp")
-                print(f"  layer {i}: {layer.get('type')}" + (f", feed-forward {ff.get('ff')}" if isinstance(ff, dict) else ", no feed-forward"))
+                if isinstance(ff, dict) and isinstance(ff.get("router"), dict):       # experts
+                    r = ff["router"]
+                    what = f", {r.get('experts')} experts of {(ff.get('expert') or {}).get('ff')}, {r.get('top')} a token"
+                else:
+                    what = f", feed-forward {ff.get('ff')}" if isinstance(ff, dict) else ", no feed-forward"
+                print(f"  layer {i}: {layer.get('type')}" + what)
         for k in ("num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
                   "intermediate_size", "vocab_size", "rope_theta", "rms_norm_eps", "tie_word_embeddings",
                   "max_position_embeddings"):
