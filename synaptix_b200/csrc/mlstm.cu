@@ -141,12 +141,341 @@ static size_t ml_walk_smem(int D, int Dv) {
 
 extern "C" int sx_mlstm_walk_fits(int D, int Dv) { return ml_walk_smem(D, Dv) <= 200 * 1024 ? 1 : 0; }
 
+// ---------------------------------------------------------------------------------------------------------------
+// pieces of ML_PIECE tokens.  Scratch: tok [T, H, 2] = (a_j = i_j - b_j, b_j) with b the running sum of f inside the
+// piece; info [S, P, H, 4] = (b_end, m_loc, m_begin, m_end); st [S, P, H, D * Dv + D]: first each piece's own sums
+// (U, then the sum of k alone), which the carry kernel replaces by the state at the piece's begin.
+// ---------------------------------------------------------------------------------------------------------------
+struct MlPieces {
+  float* tok;
+  float* info;
+  float* st;
+  int P;
+};
+
+__global__ void __launch_bounds__(ML_PIECE) mlstm_gates_kernel(MlArgs a, MlPieces w) {
+  __shared__ float gf[ML_PIECE], av[ML_PIECE];
+  pdl_wait();
+  pdl_trigger();
+  const int h = blockIdx.x, s = blockIdx.y, j = threadIdx.x, H = a.H;
+  const int t0 = a.cu_seqlens[s], len = a.cu_seqlens[s + 1] - t0;
+  float* mg = a.m + (size_t)a.seq_slots[s] * H + h;
+  float m = *mg;
+  for (int p = 0; p * ML_PIECE < len; ++p) {
+    const int L = min(ML_PIECE, len - p * ML_PIECE);
+    const int t = t0 + p * ML_PIECE + j;
+    float gi = 0.f;
+    if (j < L) {
+      gi = ml_cap(a.gates[(size_t)t * 2 * H + h] + a.bias[h], a.cap);
+      gf[j] = ml_logsigmoid(ml_cap(a.gates[(size_t)t * 2 * H + H + h] + a.bias[H + h], a.cap));
+    }
+    __syncthreads();
+    float b = 0.f;
+    if (j < L) {
+      for (int x = 0; x <= j; ++x) b += gf[x];
+      av[j] = gi - b;
+      w.tok[((size_t)t * H + h) * 2] = gi - b;
+      w.tok[((size_t)t * H + h) * 2 + 1] = b;
+    }
+    __syncthreads();
+    if (j == L - 1) {                    // b is b_end here
+      float mloc = -INFINITY;
+      for (int x = 0; x < L; ++x) mloc = fmaxf(mloc, b + av[x]);
+      const float mend = fmaxf(b + m, mloc);
+      float* o = w.info + (((size_t)s * w.P + p) * H + h) * 4;
+      o[0] = b; o[1] = mloc; o[2] = m; o[3] = mend;
+      gf[0] = mend;
+    }
+    __syncthreads();
+    m = gf[0];
+    __syncthreads();
+  }
+  if (j == 0) *mg = m;
+}
+
+// U = sum_j w_j k_j v_j^T (D x Dv) and sum_j w_j k_j (D), w_j = exp(a_j + b_end - m_loc); 4 x 4 results a thread
+template <typename T>
+__global__ void __launch_bounds__(ML_THREADS) mlstm_piece_kernel(MlArgs a, MlPieces w) {
+  extern __shared__ float sm[];
+  const int D = a.D, Dv = a.Dv, H = a.H;
+  float* ks = sm;                    // ML_PIECE * D, already times w_j
+  float* vs = ks + ML_PIECE * D;     // ML_PIECE * Dv
+  pdl_wait();
+  pdl_trigger();
+  const int p = blockIdx.x, h = blockIdx.y, s = blockIdx.z, tid = threadIdx.x;
+  const int t0 = a.cu_seqlens[s] + p * ML_PIECE, len = a.cu_seqlens[s + 1] - t0;
+  if (len <= 0) return;
+  const int L = min(ML_PIECE, len);
+  const float* info = w.info + (((size_t)s * w.P + p) * H + h) * 4;
+  const float shift = info[0] - info[1];
+  const T* proj = (const T*)a.proj;
+  for (int i = tid; i < L * D; i += ML_THREADS) {
+    const int j = i / D, d = i % D;
+    const float wj = expf(w.tok[((size_t)(t0 + j) * H + h) * 2] + shift);
+    ks[i] = to_f32(proj[(size_t)(t0 + j) * a.row + a.k_off + h * D + d]) * wj;
+  }
+  for (int i = tid; i < L * Dv; i += ML_THREADS) {
+    const int j = i / Dv, c = i % Dv;
+    vs[i] = to_f32(proj[(size_t)(t0 + j) * a.row + a.v_off + h * Dv + c]);
+  }
+  __syncthreads();
+  float* st = w.st + (((size_t)s * w.P + p) * H + h) * ((size_t)D * Dv + D);
+  const int tilesV = (Dv + 63) / 64, tilesD = (D + 15) / 16;       // a tile: 16 rows d x 64 columns, 4 x 1... see below
+  // thread (ty, tx) of a 16 x 16 grid owns rows d = 4 ty .. 4 ty + 3 (of a 64-row tile) and columns c = tx + 16 x
+  const int tx = tid & 15, ty = tid >> 4;
+  (void)tilesV; (void)tilesD;
+  for (int d0 = 0; d0 < D; d0 += 64)
+    for (int c0 = 0; c0 < Dv; c0 += 64) {
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[i][x] = 0.f;
+      for (int j = 0; j < L; ++j) {
+        float kk[4], vv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const int d = d0 + ty * 4 + i; kk[i] = d < D ? ks[j * D + d] : 0.f; }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) { const int c = c0 + tx + 16 * x; vv[x] = c < Dv ? vs[j * Dv + c] : 0.f; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int x = 0; x < 4; ++x) acc[i][x] = fmaf(kk[i], vv[x], acc[i][x]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int d = d0 + ty * 4 + i;
+        if (d >= D) continue;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int c = c0 + tx + 16 * x;
+          if (c < Dv) st[(size_t)d * Dv + c] = acc[i][x];
+        }
+      }
+    }
+  for (int d = tid; d < D; d += ML_THREADS) {
+    float acc = 0.f;
+    for (int j = 0; j < L; ++j) acc += ks[j * D + d];
+    st[(size_t)D * Dv + d] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(ML_THREADS) mlstm_carry_kernel(MlArgs a, MlPieces w) {
+  pdl_wait();
+  pdl_trigger();
+  const int H = a.H, h = blockIdx.y, s = blockIdx.z;
+  const size_t n_el = (size_t)a.D * a.Dv + a.D;
+  const size_t e = (size_t)blockIdx.x * ML_THREADS + threadIdx.x;
+  if (e >= n_el) return;
+  const int len = a.cu_seqlens[s + 1] - a.cu_seqlens[s];
+  const int slot = a.seq_slots[s];
+  float* home = e < (size_t)a.D * a.Dv ? a.S + ((size_t)slot * H + h) * a.D * a.Dv + e
+                                        : a.n + ((size_t)slot * H + h) * a.D + (e - (size_t)a.D * a.Dv);
+  float S = *home;
+  for (int p = 0; p * ML_PIECE < len; ++p) {
+    const float* info = w.info + (((size_t)s * w.P + p) * H + h) * 4;
+    const float fa = expf(info[0] + info[2] - info[3]), fb = expf(info[1] - info[3]);
+    float* u = w.st + (((size_t)s * w.P + p) * H + h) * n_el + e;
+    const float own = *u;
+    *u = S;
+    S = fa * S + fb * own;
+  }
+  *home = S;
+}
+
+// CV: columns of the result a thread owns (Dv <= 16 * CV)
+template <typename T, int CV>
+__global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPieces w) {
+  extern __shared__ float sm[];
+  const int D = a.D, Dv = a.Dv, H = a.H, DS = D + 1;
+  float* qs = sm;                        // ML_PIECE * DS
+  float* ks = qs + ML_PIECE * DS;        // ML_PIECE * DS
+  float* vs = ks + ML_PIECE * DS;        // ML_PIECE * Dv
+  float* ps = vs + ML_PIECE * Dv;        // ML_PIECE * (ML_PIECE + 1)
+  float* av = ps + ML_PIECE * (ML_PIECE + 1);   // a_j
+  float* bv = av + ML_PIECE;             // b_i
+  float* Mv = bv + ML_PIECE;             // M_i = max(m_begin, max_{j<=i} a_j)
+  float* dn = Mv + ML_PIECE;             // denominators
+  pdl_wait();
+  pdl_trigger();
+  const int p = blockIdx.x, h = blockIdx.y, s = blockIdx.z, tid = threadIdx.x;
+  const int t0 = a.cu_seqlens[s] + p * ML_PIECE, len = a.cu_seqlens[s + 1] - t0;
+  if (len <= 0) return;
+  const int L = min(ML_PIECE, len);
+  const float* info = w.info + (((size_t)s * w.P + p) * H + h) * 4;
+  const float mbeg = info[2];
+  const float* S0 = w.st + (((size_t)s * w.P + p) * H + h) * ((size_t)D * Dv + D);
+  const float* n0 = S0 + (size_t)D * Dv;
+  const T* proj = (const T*)a.proj;
+  for (int i = tid; i < ML_PIECE * D; i += ML_THREADS) {
+    const int j = i / D, d = i % D;
+    const bool ok = j < L;
+    qs[j * DS + d] = ok ? to_f32(proj[(size_t)(t0 + j) * a.row + a.q_off + h * D + d]) * a.q_scale : 0.f;
+    ks[j * DS + d] = ok ? to_f32(proj[(size_t)(t0 + j) * a.row + a.k_off + h * D + d]) : 0.f;
+  }
+  for (int i = tid; i < ML_PIECE * Dv; i += ML_THREADS) {
+    const int j = i / Dv, c = i % Dv;
+    vs[i] = j < L ? to_f32(proj[(size_t)(t0 + j) * a.row + a.v_off + h * Dv + c]) : 0.f;
+  }
+  if (tid < ML_PIECE) {
+    av[tid] = tid < L ? w.tok[((size_t)(t0 + tid) * H + h) * 2] : -INFINITY;
+    bv[tid] = tid < L ? w.tok[((size_t)(t0 + tid) * H + h) * 2 + 1] : 0.f;
+  }
+  __syncthreads();
+  if (tid < ML_PIECE) {
+    float M = mbeg;
+    for (int j = 0; j <= tid; ++j) M = fmaxf(M, av[j]);
+    Mv[tid] = M;
+  }
+  __syncthreads();
+  const int tx = tid & 15, ty = tid >> 4;
+  {   // scores: rows i = 4 ty + ii, columns j = tx + 16 x; weighted and masked
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) acc[i][x] = 0.f;
+    for (int d = 0; d < D; ++d) {
+      float qq[4], kk[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qq[i] = qs[(ty * 4 + i) * DS + d];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) kk[x] = ks[(tx + 16 * x) * DS + d];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[i][x] = fmaf(qq[i], kk[x], acc[i][x]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty * 4 + i;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const int j = tx + 16 * x;
+        ps[r * (ML_PIECE + 1) + j] = (j <= r && r < L) ? acc[i][x] * expf(av[j] - Mv[r]) : 0.f;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < ML_PIECE) {        // the denominator of row tid
+    const int r = tid;
+    float nq = 0.f;
+    for (int j = 0; j <= r; ++j) nq += ps[r * (ML_PIECE + 1) + j];
+    float n0q = 0.f;
+    for (int d = 0; d < D; ++d) n0q = fmaf(n0[d], qs[r * DS + d], n0q);
+    nq = fmaf(expf(mbeg - Mv[r]), n0q, nq);
+    dn[r] = fmaxf(fabsf(nq), expf(-(bv[r] + Mv[r]))) + a.den_eps;
+  }
+  float acc[4][CV];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int x = 0; x < CV; ++x) acc[i][x] = 0.f;
+  // the state at the piece's begin: sum_d q_i[d] S0[d][c], then times exp(m_begin - M_i)
+  for (int d = 0; d < D; ++d) {
+    float qq[4], sv[CV];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qq[i] = qs[(ty * 4 + i) * DS + d];
+#pragma unroll
+    for (int x = 0; x < CV; ++x) { const int c = tx + 16 * x; sv[x] = c < Dv ? S0[(size_t)d * Dv + c] : 0.f; }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int x = 0; x < CV; ++x) acc[i][x] = fmaf(qq[i], sv[x], acc[i][x]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float f = expf(mbeg - Mv[ty * 4 + i]);
+#pragma unroll
+    for (int x = 0; x < CV; ++x) acc[i][x] *= f;
+  }
+  const int jmax = min(L, ty * 4 + 4);
+  for (int j = 0; j < jmax; ++j) {
+    float pp[4], vv[CV];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pp[i] = ps[(ty * 4 + i) * (ML_PIECE + 1) + j];
+#pragma unroll
+    for (int x = 0; x < CV; ++x) { const int c = tx + 16 * x; vv[x] = c < Dv ? vs[j * Dv + c] : 0.f; }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int x = 0; x < CV; ++x) acc[i][x] = fmaf(pp[i], vv[x], acc[i][x]);
+  }
+  __syncthreads();             // dn[] is written
+  T* out = (T*)a.out;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    const float inv_den = 1.f / dn[r];
+    float ss = 0.f;
+#pragma unroll
+    for (int x = 0; x < CV; ++x) { acc[i][x] *= inv_den; ss += acc[i][x] * acc[i][x]; }   // columns beyond Dv hold 0
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);            // the 16 threads of a row
+    const float inv = rsqrtf(ss / (float)Dv + a.eps);
+    if (r < L) {
+      const size_t t = (size_t)(t0 + r);
+#pragma unroll
+      for (int x = 0; x < CV; ++x) {
+        const int c = tx + 16 * x;
+        if (c < Dv) {
+          const float g = to_f32(proj[t * a.row + a.g_off + h * Dv + c]);
+          out[t * H * Dv + h * Dv + c] = from_f32<T>(acc[i][x] * inv * a.gain[h * Dv + c] * ml_sigmoid(g));
+        }
+      }
+    }
+  }
+}
+
+static size_t ml_piece_smem(int D, int Dv) { return (size_t)ML_PIECE * (D + Dv) * sizeof(float); }
+static size_t ml_apply_smem(int D, int Dv) {
+  return (size_t)(2 * ML_PIECE * (D + 1) + ML_PIECE * Dv + ML_PIECE * (ML_PIECE + 1) + 4 * ML_PIECE) * sizeof(float);
+}
+
+extern "C" int sx_mlstm_piece_tokens() { return ML_PIECE; }
+extern "C" int sx_mlstm_pieces_fit(int D, int Dv) {
+  return (Dv <= 256 && ml_apply_smem(D, Dv) <= 200 * 1024 && ml_piece_smem(D, Dv) <= 200 * 1024) ? 1 : 0;
+}
+
+template <typename T>
+static int mlstm_pieces_launch(MlArgs a, MlPieces w, int n_seqs, cudaStream_t stream) {
+  const int H = a.H, D = a.D, Dv = a.Dv;
+  int rc = sx_launch(mlstm_gates_kernel, dim3(H, n_seqs), dim3(ML_PIECE), 0, stream, a, w);
+  if (rc) return rc;
+  const size_t sp = ml_piece_smem(D, Dv), sa = ml_apply_smem(D, Dv);
+  if (sp > 48 * 1024) cudaFuncSetAttribute(mlstm_piece_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp);
+  rc = sx_launch(mlstm_piece_kernel<T>, dim3(w.P, H, n_seqs), dim3(ML_THREADS), sp, stream, a, w);
+  if (rc) return rc;
+  const size_t n_el = (size_t)D * Dv + D;
+  rc = sx_launch(mlstm_carry_kernel, dim3((unsigned)((n_el + ML_THREADS - 1) / ML_THREADS), H, n_seqs), dim3(ML_THREADS), 0, stream, a, w);
+  if (rc) return rc;
+#define ML_APPLY(CV)                                                                                                          \
+  do {                                                                                                                        \
+    if (sa > 48 * 1024) cudaFuncSetAttribute(mlstm_apply_kernel<T, CV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sa); \
+    return sx_launch(mlstm_apply_kernel<T, CV>, dim3(w.P, H, n_seqs), dim3(ML_THREADS), sa, stream, a, w);                    \
+  } while (0)
+  if (Dv <= 64) ML_APPLY(4);
+  if (Dv <= 128) ML_APPLY(8);
+  ML_APPLY(16);
+#undef ML_APPLY
+}
+
 extern "C" int sx_mlstm(const void* proj, int row, int q_off, int k_off, int v_off, int g_off, const float* gates,
                         const float* bias, float cap, float q_scale, const float* gain, float eps, float den_eps,
                         float* S, float* n, float* m, void* out, const int* cu_seqlens, const int* seq_slots,
-                        int n_seqs, int H, int D, int Dv, int dt, cudaStream_t stream) {
+                        int n_seqs, int H, int D, int Dv, int dt, float* tok, float* info, float* st, int pieces,
+                        cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (H <= 0 || D <= 0 || Dv <= 0 || H > 65535 || n_seqs > 65535) return SX_ERR_SIZE;
+  if (pieces > 0) {         // long portions: pieces of ML_PIECE tokens (the caller has asked sx_mlstm_pieces_fit)
+    if (!sx_mlstm_pieces_fit(D, Dv) || tok == nullptr || info == nullptr || st == nullptr) return SX_ERR_SIZE;
+    MlArgs a = {proj, row, q_off, k_off, v_off, g_off, gates, bias, cap, q_scale, eps, den_eps, gain, S, n, m, out,
+                cu_seqlens, seq_slots, H, D, Dv};
+    MlPieces w = {tok, info, st, pieces};
+    if (dt == SX_F32) return mlstm_pieces_launch<float>(a, w, n_seqs, stream);
+    if (dt == SX_BF16) return mlstm_pieces_launch<bf16>(a, w, n_seqs, stream);
+    return SX_ERR_DTYPE;
+  }
   const size_t smem = ml_walk_smem(D, Dv);
   if (smem > 200 * 1024) return SX_ERR_SIZE;
   MlArgs a = {proj, row, q_off, k_off, v_off, g_off, gates, bias, cap, q_scale, eps, den_eps, gain, S, n, m, out,

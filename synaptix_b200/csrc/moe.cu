@@ -10,7 +10,9 @@
 //                      finds it from `offsets`; tiles beyond the last return).  GATE_UP: rows are gathered from x by
 //                      pair / top, the expert's [gate; up] matrix gives two accumulators and the result is
 //                      silu(gate) * up  [T * top, ff] in sorted order; else rows are read in sorted order and the
-//                      result is the plain product [T * top, N].  64x64x16 tiles, 4x4 results a thread, 32-bit FFMA.
+//                      result is the plain product [T * top, N].  64x64x16 tiles, 4x4 results a thread, 32-bit FFMA
+//                      (float32, and bfloat16 with K % 8 != 0).
+//   moe_mma_kernel     the same product for bfloat16 on the tensor cores (see there).
 //   moe_combine_kernel out[t] = sum_j weights[t, j] * y[place[t * top + j]], the choices in their order.
 #include "common.cuh"
 
@@ -205,6 +207,178 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same grouped product for bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit accumulation): a block of 8
+// warps (2 along the rows x 4 along the columns) owns 64 rows x 128 matrix rows; with GATE_UP these are 64 gate rows
+// and the 64 up rows of the same outputs, so a thread holds gate and up of one place and the activation needs no
+// exchange.  Rows of x (gathered through `order`) and of the expert's matrix come by cp.async, 16 bytes a copy,
+// through a ring of MM_STAGES stages of 32 k each; fragments by ldmatrix from rows padded to 80 bytes.  With a few
+// rows per expert (single-token steps) a block still streams its 128 matrix rows once: the kernel is then bound by
+// the experts' weights, which each active expert's blocks read exactly once.  K % 8 == 0.
+// ---------------------------------------------------------------------------------------------------------------
+#define MM_BM 64
+#define MM_BN 128
+#define MM_BK 32
+#define MM_LD 40             // elements of a staged row (32 + 8 of padding)
+#define MM_STAGES 4
+
+__device__ __forceinline__ void mm_cp16(void* smem, const void* gmem, bool ok) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem);
+  const int n = ok ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void mm_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void mm_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void mm_ldsm4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TC, bool GATE_UP>
+__global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ Wt, TC* __restrict__ C,
+                                                      const int* __restrict__ offsets, const int* __restrict__ order,
+                                                      int E, int N, int K, int top) {
+  extern __shared__ __align__(16) unsigned char mm_smem[];
+  bf16* As = (bf16*)mm_smem;                                        // MM_STAGES * MM_BM * MM_LD
+  bf16* Ws = As + MM_STAGES * MM_BM * MM_LD;                        // MM_STAGES * MM_BN * MM_LD
+  __shared__ int src[MM_BM];
+  __shared__ int which[3];
+  pdl_wait();
+  pdl_trigger();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    int tile = blockIdx.y, e = 0, r0 = -1;
+    for (; e < E; ++e) {
+      const int n_e = offsets[e + 1] - offsets[e];
+      const int tiles = (n_e + MM_BM - 1) / MM_BM;
+      if (tile < tiles) { r0 = offsets[e] + tile * MM_BM; break; }
+      tile -= tiles;
+    }
+    which[0] = e; which[1] = r0; which[2] = r0 >= 0 ? min(MM_BM, offsets[e + 1] - r0) : 0;
+  }
+  __syncthreads();
+  const int e = which[0], r0 = which[1], nr = which[2];
+  if (r0 < 0) return;
+  if (tid < MM_BM) src[tid] = tid < nr ? (GATE_UP ? order[r0 + tid] / top : r0 + tid) : -1;
+  __syncthreads();
+  constexpr int NOUT = GATE_UP ? MM_BN / 2 : MM_BN;                 // output columns of a block
+  const int n0 = blockIdx.x * NOUT;
+  const bf16* We = Wt + (size_t)e * (GATE_UP ? 2 : 1) * N * K;
+  // what this thread copies each stage: one 16-byte piece of x and two of the matrix
+  const int a_row = tid >> 2, a_ch = tid & 3;
+  const bf16* a_src = A + (size_t)max(src[a_row], 0) * K + a_ch * 8;
+  const bool a_ok = src[a_row] >= 0;
+  const bf16* w_src[2];
+  bool w_ok[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (tid + i * 256) >> 2;                              // row of the staged tile
+    int n;                                                           // row of the expert's matrix
+    bool ok;
+    if (GATE_UP) { const int c = n0 + (r & 63); ok = c < N; n = (r < 64 ? 0 : N) + c; }
+    else { n = n0 + r; ok = n < N; }
+    w_ok[i] = ok;
+    w_src[i] = We + (size_t)(ok ? n : 0) * K + a_ch * 8;
+  }
+  const int nk = (K + MM_BK - 1) / MM_BK;
+  auto load = [&](int kt, int stage) {
+    const int k0 = kt * MM_BK;
+    const bool kin = k0 + a_ch * 8 < K;
+    mm_cp16(As + ((size_t)stage * MM_BM + a_row) * MM_LD + a_ch * 8, a_src + k0, a_ok && kin);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      mm_cp16(Ws + ((size_t)stage * MM_BN + ((tid + i * 256) >> 2)) * MM_LD + a_ch * 8, w_src[i] + k0, w_ok[i] && kin);
+  };
+#pragma unroll
+  for (int s = 0; s < MM_STAGES - 1; ++s) {
+    if (s < nk) load(s, s);
+    mm_commit();
+  }
+  const int wm = warp >> 2, wn = warp & 3;                           // 2 x 4 warps; a warp: 32 rows x 4 n8 tiles
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) acc[i][j][x] = 0.f;
+  for (int kt = 0; kt < nk; ++kt) {
+    mm_wait<MM_STAGES - 2>();
+    __syncthreads();                                                 // stage kt has landed; stage kt - 1 is read out
+    if (kt + MM_STAGES - 1 < nk) load(kt + MM_STAGES - 1, (kt + MM_STAGES - 1) % MM_STAGES);
+    mm_commit();
+    const bf16* as = As + (size_t)(kt % MM_STAGES) * MM_BM * MM_LD;
+    const bf16* ws = Ws + (size_t)(kt % MM_STAGES) * MM_BN * MM_LD;
+#pragma unroll
+    for (int kk = 0; kk < MM_BK / 16; ++kk) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+        mm_ldsm4(af[mi][0], af[mi][1], af[mi][2], af[mi][3],
+                 as + (size_t)(wm * 32 + mi * 16 + (lane & 15)) * MM_LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {                         // two n8 tiles a load
+        // GATE_UP: pair 0 = this warp's 16 gate rows (staged rows wn * 16 ..), pair 1 = its 16 up rows (64 + wn * 16 ..)
+        const int nb = GATE_UP ? pair * 64 + wn * 16 : wn * 32 + pair * 16;
+        uint32_t b0, b1, b2, b3;
+        mm_ldsm4(b0, b1, b2, b3, ws + (size_t)(nb + (lane & 7) + (lane >> 4) * 8) * MM_LD + kk * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+          mm_mma(acc[mi][pair * 2], af[mi], b0, b1);
+          mm_mma(acc[mi][pair * 2 + 1], af[mi], b2, b3);
+        }
+      }
+    }
+  }
+  mm_wait<0>();
+  const int row_in = lane >> 2, col_in = (lane & 3) * 2;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + mi * 16 + half * 8 + row_in;
+      if (r >= nr) continue;
+      TC* crow = C + (size_t)(r0 + r) * N;
+      if (GATE_UP) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int n = n0 + wn * 16 + j * 8 + col_in + x;
+            if (n < N) crow[n] = from_f32<TC>(moe_silu(acc[mi][j][half * 2 + x]) * acc[mi][2 + j][half * 2 + x]);
+          }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int n = n0 + wn * 32 + j * 8 + col_in + x;
+            if (n < N) crow[n] = from_f32<TC>(acc[mi][j][half * 2 + x]);
+          }
+      }
+    }
+}
+
+template <typename TC, bool GATE_UP>
+static int moe_mma_launch(const void* A, const void* Wt, void* C, const int* offsets, const int* order, int tiles, int E, int N,
+                          int K, int top, cudaStream_t stream) {
+  const size_t smem = (size_t)MM_STAGES * (MM_BM + MM_BN) * MM_LD * sizeof(bf16);
+  static bool set = false;
+  if (!set) {
+    cudaError_t err = cudaFuncSetAttribute(moe_mma_kernel<TC, GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    set = true;
+  }
+  const int nout = GATE_UP ? MM_BN / 2 : MM_BN;
+  dim3 grid((N + nout - 1) / nout, tiles);
+  return sx_launch(moe_mma_kernel<TC, GATE_UP>, grid, dim3(256), smem, stream, (const bf16*)A, (const bf16*)Wt, (TC*)C, offsets,
+                   order, E, N, K, top);
+}
+
 // rows: T * top; the grid's y axis has room for every expert's last, partly filled tile
 extern "C" int sx_moe_gemm(const void* A, const void* Wt, void* C, const int* offsets, const int* order, int rows, int E, int N,
                            int K, int top, int gate_up, int a_dt, int c_dt, cudaStream_t stream) {
@@ -212,6 +386,11 @@ extern "C" int sx_moe_gemm(const void* A, const void* Wt, void* C, const int* of
   if (E <= 0 || N <= 0 || K <= 0) return SX_ERR_SIZE;
   const int tiles = (rows + 63) / 64 + (E < rows ? E : rows);
   if (tiles > 65535) return SX_ERR_SIZE;
+  if (a_dt == SX_BF16 && K % 8 == 0 && ((uintptr_t)A | (uintptr_t)Wt) % 16 == 0) {       // the tensor cores
+    if (gate_up && c_dt == SX_BF16) return moe_mma_launch<bf16, true>(A, Wt, C, offsets, order, tiles, E, N, K, top, stream);
+    if (!gate_up && c_dt == SX_F32) return moe_mma_launch<float, false>(A, Wt, C, offsets, order, tiles, E, N, K, top, stream);
+    if (!gate_up && c_dt == SX_BF16) return moe_mma_launch<bf16, false>(A, Wt, C, offsets, order, tiles, E, N, K, top, stream);
+  }
   dim3 grid((N + 63) / 64, tiles);
 #define MOE_GO(TA, TC, GU) return sx_launch(moe_gemm_kernel<TA, TA, TC, GU>, grid, dim3(256), 0, stream, (const TA*)A, (const TA*)Wt, (TC*)C, offsets, order, E, N, K, top)
   if (gate_up) {

@@ -257,7 +257,7 @@ def test_latent_attention_layer_against_per_head_keys_and_values(dtype, pairs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,experts,top,ff,width", [(1, 5, 2, 24, 52), (3, 1, 1, 16, 40), (70, 7, 7, 40, 64), (300, 16, 4, 100, 130), (9, 12, 3, 64, 320)])
+@pytest.mark.parametrize("T,experts,top,ff,width", [(1, 5, 2, 24, 52), (3, 1, 1, 16, 40), (70, 7, 7, 40, 64), (300, 16, 4, 100, 130), (9, 12, 3, 64, 320), (400, 6, 2, 136, 264)])
 def test_mixture_of_experts(T, experts, top, ff, width, dtype):
     """Router, sort by expert, grouped products and the weighted sum against the plain form; one token's input is made
     to fall on a near tie of the router, which the comparison leaves out."""
