@@ -306,3 +306,111 @@ extern "C" int sx_latent_output(const float* ol, const void* wuv, int H, int Dv,
                      (const bf16*)proj, row, col_g, (bf16*)y, T);
   return SX_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Whole prompts with per-head keys and values (the form that a tensor-core attention kernel over paged keys and values
+// takes): the step's latents are gathered from the cache, one product makes every head's unrotated keys and values
+// from them, and these kernels lay them out.
+//   latent_gather_kernel   c [T, R] and k_rot [T, Dr] of the step's tokens out of their cache rows
+//   latent_expand_kernel   kv [T, H * D + H * Dv] (the product's result) and k_rot -> key pages [P, H, 64, D + Dr] =
+//                          [k_h | k_rot] and value pages [P, H, 64, Dv], token t of sequence s in page
+//                          table[s, pos / 64] at row pos % 64
+//   latent_rotate_q_kernel the rotated part of every query head rotated in place ([T, H, D + Dr])
+//   head_gate_kernel       y[t, h, :] *= sigmoid(proj[t, col + h])
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ k_pages, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int maxp,
+                                     int R, int Dr, T* __restrict__ c, T* __restrict__ kr) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, pos = positions[t];
+  const int page = block_table[(size_t)seq_of_token[t] * maxp + (pos >> 6)];
+  const T* row = k_pages + ((size_t)page * SX_PAGE + (pos & 63)) * (R + Dr);
+  for (int i = threadIdx.x; i < R; i += blockDim.x) c[(size_t)t * R + i] = row[i];
+  for (int i = threadIdx.x; i < Dr; i += blockDim.x) kr[(size_t)t * Dr + i] = row[R + i];
+}
+
+template <typename T>
+__global__ void latent_expand_kernel(const T* __restrict__ kv, const T* __restrict__ kr, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_of_token, const int* __restrict__ table, int maxp, int H, int D,
+                                     int Dr, int Dv, T* __restrict__ kp, T* __restrict__ vp) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, pos = positions[t];
+  const int page = table[(size_t)seq_of_token[t] * maxp + (pos >> 6)];
+  const int E = D + Dr, row = pos & 63;
+  const T* src = kv + (size_t)t * (H * D + H * Dv);
+  for (int i = threadIdx.x; i < H * E; i += blockDim.x) {
+    const int h = i / E, e = i % E;
+    kp[(((size_t)page * H + h) * SX_PAGE + row) * E + e] = e < D ? src[h * D + e] : kr[(size_t)t * Dr + (e - D)];
+  }
+  for (int i = threadIdx.x; i < H * Dv; i += blockDim.x) {
+    const int h = i / Dv, e = i % Dv;
+    vp[(((size_t)page * H + h) * SX_PAGE + row) * Dv + e] = src[H * D + i];
+  }
+}
+
+template <typename T>
+__global__ void latent_rotate_q_kernel(T* __restrict__ q, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                       int dims, int pairs, int H, int D, int Dr) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  const int half = dims / 2;
+  for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+    const int h = i / half, p = i % half;
+    int ia, ib;
+    rot_pair_index(p, dims, pairs, ia, ib);
+    T* qr = q + ((size_t)t * H + h) * (D + Dr) + D;
+    float sn, cs;
+    sincosf(pos * inv_freq[p], &sn, &cs);
+    const float u = to_f32(qr[ia]), v = to_f32(qr[ib]);
+    qr[ia] = from_f32<T>(u * cs - v * sn);
+    qr[ib] = from_f32<T>(v * cs + u * sn);
+  }
+}
+
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ y, const T* __restrict__ proj, int row, int col, int H, int Dv) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H * Dv; i += blockDim.x) {
+    const float g = 1.f / (1.f + expf(-to_f32(proj[(size_t)t * row + col + i / Dv])));
+    y[(size_t)t * H * Dv + i] = from_f32<T>(to_f32(y[(size_t)t * H * Dv + i]) * g);
+  }
+}
+
+extern "C" int sx_latent_gather(const void* k_pages, const int* positions, const int* seq_of_token, const int* block_table,
+                                int maxp, int R, int Dr, void* c, void* kr, int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dt == SX_F32) return sx_launch(latent_gather_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)k_pages, positions, seq_of_token, block_table, maxp, R, Dr, (float*)c, (float*)kr);
+  if (dt == SX_BF16) return sx_launch(latent_gather_kernel<bf16>, dim3(T), dim3(256), 0, stream, (const bf16*)k_pages, positions, seq_of_token, block_table, maxp, R, Dr, (bf16*)c, (bf16*)kr);
+  return SX_ERR_DTYPE;
+}
+
+extern "C" int sx_latent_expand(const void* kv, const void* kr, const int* positions, const int* seq_of_token, const int* table,
+                                int maxp, int H, int D, int Dr, int Dv, void* kp, void* vp, int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dt == SX_F32) return sx_launch(latent_expand_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)kv, (const float*)kr, positions, seq_of_token, table, maxp, H, D, Dr, Dv, (float*)kp, (float*)vp);
+  if (dt == SX_BF16) return sx_launch(latent_expand_kernel<bf16>, dim3(T), dim3(256), 0, stream, (const bf16*)kv, (const bf16*)kr, positions, seq_of_token, table, maxp, H, D, Dr, Dv, (bf16*)kp, (bf16*)vp);
+  return SX_ERR_DTYPE;
+}
+
+extern "C" int sx_latent_rotate_q(void* q, const int* positions, const float* inv_freq, int dims, int pairs, int H, int D, int Dr,
+                                  int T, int dt, cudaStream_t stream) {
+  if (T <= 0 || dims <= 0) return 0;
+  if (dims > Dr || (dims & 1)) return SX_ERR_SIZE;
+  if (dt == SX_F32) return sx_launch(latent_rotate_q_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)q, positions, inv_freq, dims, pairs, H, D, Dr);
+  if (dt == SX_BF16) return sx_launch(latent_rotate_q_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)q, positions, inv_freq, dims, pairs, H, D, Dr);
+  return SX_ERR_DTYPE;
+}
+
+extern "C" int sx_head_gate(void* y, const void* proj, int row, int col, int H, int Dv, int T, int dt, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dt == SX_F32) return sx_launch(head_gate_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)y, (const float*)proj, row, col, H, Dv);
+  if (dt == SX_BF16) return sx_launch(head_gate_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)y, (const bf16*)proj, row, col, H, Dv);
+  return SX_ERR_DTYPE;
+}

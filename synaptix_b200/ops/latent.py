@@ -84,3 +84,50 @@ def latent_output(ol: torch.Tensor, wuv: torch.Tensor, heads: int, vdim: int, kv
                                            c_int(proj.shape[1]), c_int(col_gate), ptr(y), c_int(T), c_int(dt_code(out_dtype)),
                                            stream()), "latent_output")
     return y
+
+
+def latent_gather(k_pages: torch.Tensor, ctx, block_table: torch.Tensor, kv_rank: int, rot_dim: int):
+    """The cache rows of the step's own tokens: ``c [T, kv_rank]`` and ``k_rot [T, rot_dim]`` in the cache's dtype."""
+    require_cuda(k_pages, block_table)
+    T = ctx.n_tokens
+    c = torch.empty((T, kv_rank), dtype=k_pages.dtype, device=k_pages.device)
+    kr = torch.empty((T, rot_dim), dtype=k_pages.dtype, device=k_pages.device)
+    check(fn("latent", "sx_latent_gather")(ptr(k_pages), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
+                                           c_int(block_table.shape[1]), c_int(kv_rank), c_int(rot_dim), ptr(c), ptr(kr), c_int(T),
+                                           c_int(dt_code(k_pages.dtype)), stream()), "latent_gather")
+    return c, kr
+
+
+def latent_expand(kv: torch.Tensor, kr: torch.Tensor, ctx, table: torch.Tensor, heads: int, dim: int, rot_dim: int, vdim: int,
+                  k_out: torch.Tensor, v_out: torch.Tensor) -> None:
+    """Per-head keys ``[k_h | k_rot]`` and values of the step's tokens into pages ``k_out [P, heads, 64, dim + rot_dim]``,
+    ``v_out [P, heads, 64, vdim]`` by the page table ``table [S, pages]``; ``kv [T, heads * dim + heads * vdim]`` holds
+    every head's unrotated key, then every head's value."""
+    require_cuda(kv, kr, table, k_out, v_out)
+    T = kv.shape[0]
+    if (kv.shape[1] != heads * (dim + vdim) or tuple(k_out.shape[1:]) != (heads, 64, dim + rot_dim)
+            or tuple(v_out.shape[1:]) != (heads, 64, vdim) or tuple(kr.shape) != (T, rot_dim)):
+        raise KernelError("latent_expand: sizes do not fit")
+    check(fn("latent", "sx_latent_expand")(ptr(kv), ptr(kr), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(table),
+                                           c_int(table.shape[1]), c_int(heads), c_int(dim), c_int(rot_dim), c_int(vdim),
+                                           ptr(k_out), ptr(v_out), c_int(T), c_int(dt_code(kv.dtype)), stream()), "latent_expand")
+
+
+def latent_rotate_q(q: torch.Tensor, heads: int, dim: int, rot_dim: int, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                    pairs: bool, ctx) -> None:
+    """The rotated part of every query head of ``q [T, heads * (dim + rot_dim)]`` rotated in place."""
+    require_cuda(q, inv_freq)
+    if inv_freq is None or rot_dims == 0:
+        return
+    check(fn("latent", "sx_latent_rotate_q")(ptr(q), ptr(ctx.positions), ptr(inv_freq), c_int(rot_dims), c_int(1 if pairs else 0),
+                                             c_int(heads), c_int(dim), c_int(rot_dim), c_int(q.shape[0]), c_int(dt_code(q.dtype)),
+                                             stream()), "latent_rotate_q")
+
+
+def head_gate(y: torch.Tensor, proj: torch.Tensor, col: int, heads: int, vdim: int) -> None:
+    """``y[t, h, :] *= sigmoid(proj[t, col + h])`` in place (``y [T, heads * vdim]``)."""
+    require_cuda(y, proj)
+    if y.dtype != proj.dtype or y.shape[1] != heads * vdim or col + heads > proj.shape[1]:
+        raise KernelError("head_gate: sizes or dtypes do not fit")
+    check(fn("latent", "sx_head_gate")(ptr(y), ptr(proj), c_int(proj.shape[1]), c_int(col), c_int(heads), c_int(vdim),
+                                       c_int(y.shape[0]), c_int(dt_code(y.dtype)), stream()), "head_gate")

@@ -14,6 +14,11 @@ weighted latent afterwards.  The cache therefore holds keys only (``KVRequest(ke
 ``kv_rank + rot_dim`` elements; the values are its first ``kv_rank`` elements.  Queries in the latent's space and the
 weighted latents stay 32-bit.
 
+Whole prompts in bfloat16 whose head sizes a tensor-core attention kernel takes (``dim + rot_dim == vdim`` of 32, 64 or
+128) run the other form instead: the step's latents are read back from the cache, ONE product with ``[Wuk; Wuv]`` makes
+all heads' keys and values, which go into pages of the step's own with the rotated part behind each head's key, and the
+library's attention over paged keys and values runs on them (``ops.attention``); nothing of it outlasts the step.
+
 A layer built with ``own_kv=False`` has no ``Wdkv``: the schedule gives it the cache entry of the layer whose latent
 it reads (``LayerRun(..., write_cache=False)``); its ``Wuk``, ``Wuv``, queries, window and gate are its own.
 """
@@ -86,6 +91,50 @@ class LatentAttention(Mixer):
             self.dkv_gain = to_device_f32(tensors[p + n["dkv_norm"]], rt)
         self.uk = to_device_matrix(tensors[p + n["uk"]], rt)          # [heads * dim, kv_rank]
         self.uv = to_device_matrix(tensors[p + n["uv"]], rt)          # [heads * vdim, kv_rank]
+        self.ukv = torch.cat([self.uk, self.uv], dim=0).contiguous() if self._per_head_form_fits(rt.dtype) else None
+
+    # prompts of fewer tokens run the latent form: its kernels cost less than the per-head form's products and launches
+    PER_HEAD_MIN_TOKENS = 256
+
+    def _per_head_form_fits(self, dtype) -> bool:
+        return (dtype == torch.bfloat16 and self.dim + self.rot_dim == self.vdim and self.vdim in (32, 64, 128)
+                and self.heads <= 65535 and self.kv_rank % 8 == 0)
+
+    def _whole_prompts(self, ctx: StepContext) -> bool:
+        return (self.ukv is not None and ctx.host is not None and not ctx.all_single
+                and ctx.n_tokens >= self.PER_HEAD_MIN_TOKENS and all(p == 0 for p in ctx.host["seq_past"]))
+
+    def _step_pages(self, ctx: StepContext, device):
+        """Pages of the step's own for per-head keys and values: a table ``[S, pages]`` (made once a step) that gives
+        every sequence consecutive pages from 1 on (page 0 stands where a sequence has none), and how many there are."""
+        made = ctx.scratch.get("latent_step_pages")
+        if made is None:
+            import numpy as np
+            lens = ctx.host["seq_lens"]
+            maxp = max((n + 63) // 64 for n in lens)
+            table = np.zeros((len(lens), maxp), dtype=np.int32)
+            nxt = 1
+            for i, n in enumerate(lens):
+                k = (n + 63) // 64
+                table[i, :k] = np.arange(nxt, nxt + k)
+                nxt += k
+            made = ctx.scratch["latent_step_pages"] = (torch.from_numpy(table).to(device, non_blocking=True), nxt)
+        return made
+
+    def _forward_per_head(self, x, p, q, ctx: StepContext, cache_view: KVView, bt, inv_freq, rot_dims, pairs):
+        H, D, Dr, Dv = self.heads, self.dim, self.rot_dim, self.vdim
+        c, kr = ops.latent_gather(cache_view.k, ctx, bt, self.kv_rank, Dr)
+        kv = ops.linear(c, self.ukv)
+        table, n_pages = self._step_pages(ctx, x.device)
+        # zeros: the rows behind a sequence's end are masked, but a tensor-core product still multiplies them
+        kp = torch.zeros((n_pages, H, 64, D + Dr), dtype=x.dtype, device=x.device)
+        vp = torch.zeros((n_pages, H, 64, Dv), dtype=x.dtype, device=x.device)
+        ops.latent_expand(kv, kr, ctx, table, H, D, Dr, Dv, kp, vp)
+        ops.latent_rotate_q(q, H, D, Dr, inv_freq, rot_dims, pairs, ctx)
+        y = ops.attention(q, kp, vp, ctx, table, H, H, D + Dr, self.scale, self.window)
+        if self.gated:
+            ops.head_gate(y, p, self.col_g, H, Dv)
+        return self.o.forward(y)
 
     def cache_request(self):
         if not self.own_kv:
@@ -103,6 +152,8 @@ class LatentAttention(Mixer):
         cq = ops.latent_prepare(p, self.q_rank, self.col_dkv, self.kv_rank, self.rot_dim, self.dq_gain, self.dkv_gain,
                                 self.norm_eps, inv_freq, rot_dims, pairs, ctx, bt, cache_view.k if write_cache else None)
         q = self.uq.forward(cq)
+        if self._whole_prompts(ctx):
+            return self._forward_per_head(x, p, q, ctx, cache_view, bt, inv_freq, rot_dims, pairs)
         qa = ops.latent_query(q, self.uk, self.heads, self.dim, self.rot_dim, self.kv_rank, inv_freq, rot_dims, pairs, ctx)
         ol = ops.latent_attention(qa, cache_view.k, ctx, bt, self.heads, self.kv_rank, self.rot_dim, self.scale, self.window)
         y = ops.latent_output(ol, self.uv, self.heads, self.vdim, self.kv_rank, p, self.col_g, x.dtype)

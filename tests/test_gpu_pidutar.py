@@ -14,7 +14,7 @@ from tiny_pidutar import CONFIGS, folder, oracle, oracle_logits
 
 pytestmark = pytest.mark.gpu
 
-NAMES = ["PA", "PB", "PF"]
+NAMES = ["PA", "PB", "PF", "PT"]
 DTYPES = ["float32", "bfloat16"]
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
@@ -320,12 +320,34 @@ def test_whole_prompts_every_place(engines, name, dtype):
     from synaptix_b200.engine import Entry
     eng = engines(name, dtype)
     assert type(eng.model.config).__name__ == "PidutarConfig" and eng.use_graphs
-    for i, n in enumerate([1, 2, 3, 17, 64, 65, 150, 301]):
+    for i, n in enumerate([1, 2, 3, 17, 64, 65, 150, 301, 700]):
         toks = random_tokens(vocab(name), n, 100 + i)
         s = eng.open()
         got = eng.step([Entry(s, toks, list(range(n)))])
         eng.close(s)
         assert_close(got, oracle_logits(name, tuple(toks)), dtype, f"{name} {dtype} whole n={n}")
+
+
+def test_whole_prompts_in_bfloat16_take_the_per_head_form(engines, monkeypatch):
+    """Head sizes a tensor-core attention kernel takes: a whole prompt of 256 tokens and more goes through per-head keys
+    and values in pages of the step's own (two of the three attention layers of this model), a shorter one, a portion
+    behind cached tokens and single tokens through the latent form; all agree with the plain implementation."""
+    from synaptix_b200 import ops
+    from synaptix_b200.engine import Entry
+    calls = []
+    orig = ops.latent_expand
+    monkeypatch.setattr(ops, "latent_expand", lambda *a, **k: (calls.append(1), orig(*a, **k))[1])
+    eng = engines("PT", "bfloat16")
+    toks = random_tokens(vocab("PT"), 400, 5)
+    ref = oracle_logits("PT", tuple(toks))
+    s = eng.open()
+    got = [eng.step([Entry(s, toks[:300], list(range(300)))])]
+    assert len(calls) == 2
+    got.append(eng.step([Entry(s, toks[300:399], list(range(99)))]))
+    got.append(eng.step([Entry(s, toks[399:], [0])]))
+    assert len(calls) == 2
+    eng.close(s)
+    assert_close(torch.cat(got), ref, "bfloat16", "PT: per-head form, then the latent form")
 
 
 @pytest.mark.parametrize("name", NAMES)

@@ -60,7 +60,17 @@ PF = dict(architecture="Pidutar", vocab=256, width=128, norm=dict(eps=1e-5), emb
                   _mem(4, 64, 32, 8.0, _moe(96, 4, 3, 1.0))])
 PF_INIT = dict(seed=13, std_matrix=0.08, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
 
-CONFIGS = {"PA": (PA, PA_INIT), "PB": (PB, PB_INIT), "PF": (PF, PF_INIT)}
+# head sizes that the tensor-core attention over per-head keys and values takes (dim + rot_dim = vdim = 64 and 128):
+# whole prompts of 256 tokens and more run that form in bfloat16; a reader with wider heads than its owner and no window
+PT = dict(architecture="Pidutar", vocab=160, width=128, norm=dict(eps=1e-5), embedding=dict(scale=3.0), residual_mult=0.3,
+          logit_scale=0.25,
+          layers=[_lat(4, 32, 32, 64, 64, 64, 0.125, 100, (32, 1.0e6), _moe(64, 4, 2, 2.0)),
+                  _mem(2, 32, 32, 10.0, _moe(64, 4, 2, 2.0)),
+                  _lat(2, 96, 32, 128, 32, 64, 0.09, None, (32, 1.0e6), _moe(64, 4, 2, 2.0), kv_from=0),
+                  _lat(3, 48, 16, 64, 48, 40, 0.12, 64, (8, 1.0e4), None)])
+PT_INIT = dict(seed=17, std_matrix=0.08, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
+
+CONFIGS = {"PA": (PA, PA_INIT), "PB": (PB, PB_INIT), "PF": (PF, PF_INIT), "PT": (PT, PT_INIT)}
 
 _FOLDERS = {}
 
