@@ -243,9 +243,30 @@ def vemedra_config(width, ff, nh, nkv, hd, rh, runs, vocab):
                 loop=dict(start=0, stop=2, times=2))
 
 
+def pidutar_config(width, ff, nh, nkv, hd, rh, runs, vocab):
+    """``runs`` layers (mlstm, latent attention, a latent attention that reads the one before, latent attention) repeated:
+    ``rh`` memory heads of ``hd x hd``; attention heads of ``hd/2`` unrotated and ``hd/2`` rotated elements with values
+    of ``hd``, latents of ``width/8`` (queries ``width/2``), windows of 1,000; 16 experts of ``ff/4``, 4 a token (as many
+    active feed-forward weights as the dense models beside it)."""
+    mem = dict(type="mlstm", mixer=dict(heads=rh, dim=hd, vdim=hd, gate_cap=15.0))
+    att = dict(heads=nh, dim=hd // 2, rot_dim=hd // 2, vdim=hd, q_rank=width // 2, kv_rank=width // 8, scale=hd ** -0.5,
+               mask=dict(size=1000), rot=dict(dims=hd // 2, base=1.0e6))
+    mlp = dict(kind="moe", expert=dict(ff=ff // 4), router=dict(experts=16, top=4, scale=1.0))
+    layers = []
+    for i in range(runs):
+        if i % 4 == 0:
+            layers.append(dict(mem, mlp=mlp))
+        elif i % 4 == 2:
+            layers.append(dict(type="latent_attention", mixer=dict(att, kv_from=i - 1), mlp=mlp))
+        else:
+            layers.append(dict(type="latent_attention", mixer=att, mlp=mlp))
+    return dict(architecture="Pidutar", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                residual_mult=0.5, logit_scale=1.0, layers=layers)
+
+
 def arch_points(torch, a):
     from synaptix_b200.api import LLM
-    from synaptix_b200.config import Qwen3Config, VemedraConfig
+    from synaptix_b200.config import PidutarConfig, Qwen3Config, VemedraConfig
     from synaptix_b200.engine import DecodeRow, Entry
     from synaptix_b200.models import model_skeleton
     from synaptix_b200.parts import Runtime
@@ -304,11 +325,14 @@ def arch_points(torch, a):
 
     for name in (a.arch_sizes.split(",") if a.arch_sizes else list(VEMEDRA_SIZES)):
         width, ff, nh, nkv, hd, rh = VEMEDRA_SIZES[name]
+        if a.arch == "pidutar":
+            measure(PidutarConfig.from_dict(pidutar_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"pidutar_{name}")
         measure(VemedraConfig.from_dict(vemedra_config(width, ff, nh, nkv, hd, rh, RUNS, VOCAB)), f"vemedra_{name}")
         measure(Qwen3Config.from_dict(dict(QWEN3_4B, num_hidden_layers=RUNS, hidden_size=width, num_attention_heads=nh,
                                            num_key_value_heads=nkv, head_dim=hd, intermediate_size=ff, vocab_size=VOCAB,
                                            tie_word_embeddings=False)), f"qwen3_{name}")
-    return {"metric": "prompt step and decode step, Vemedra beside Qwen3 at equal sizes (bf16, random weights)", "impl": "ours",
+    return {"metric": f"prompt step and decode step, {'Pidutar beside Vemedra and' if a.arch == 'pidutar' else 'Vemedra beside'} "
+                      "Qwen3 at equal sizes (bf16, random weights)", "impl": "ours",
             "layer_runs": RUNS, "vocab": VOCAB, "context": CONTEXT, "steps": K, "warmup": a.warmup, "sizes": VEMEDRA_SIZES,
             "data": "synthetic", "dtype": "bf16", "points": out}
 
@@ -334,9 +358,10 @@ def main():
     ap.add_argument("--short", action="store_true",
                     help="decode only 5 x --steps + --warmup tokens instead of at least 255 (small cases for profilers: "
                          "every launch under a profiler costs a good part of a second)")
-    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra"],
-                    help="vemedra: the Vemedra decoder beside Qwen3 at equal sizes (prompt step, decode at batch 1 and 8) instead of the default run")
-    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra: which of 1k,2.5k,4k (default: all)")
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "vemedra", "pidutar"],
+                    help="vemedra: the Vemedra decoder beside Qwen3 at equal sizes (prompt step, decode at batch 1 and 8) instead of "
+                         "the default run; pidutar: the Pidutar decoder beside both")
+    ap.add_argument("--arch-sizes", default="", help="with --arch vemedra or pidutar: which of 1k,2.5k,4k (default: all)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -350,7 +375,7 @@ def main():
     a.warmup = max(a.warmup, 3)
 
     import torch
-    if a.arch == "vemedra":
+    if a.arch in ("vemedra", "pidutar"):
         a.steps = min(a.steps, 40)
         print(json.dumps(arch_points(torch, a)))
         return 0

@@ -44,6 +44,7 @@ LIBRARIES: Dict[str, tuple] = {
     "mlstm": ("mlstm.cu", []),
     "latent": ("latent.cu", []),
     "moe": ("moe.cu", []),
+    "moe_tc": ("moe_tc.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
     "attn_decode": ("attn_decode.cu", []),

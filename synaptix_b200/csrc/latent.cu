@@ -14,8 +14,9 @@
 //   latent_attn_kernel     one block a (token, group of 8 heads), a warp a head: key rows of the window staged in shared
 //                          memory 32 at a time for all heads of the block; a lane scores one key, the softmax runs
 //                          over the warp, and the weighted sum of c has a lane own the elements r = lane, lane + 32, ...
-//                          -> float32 [T, H, R]
-//   latent_output_kernel   one block a (tile of 8 tokens, head): y[h Dv + j] = sigmoid(gate_h) * sum_r Wuv[h Dv + j, r] o'[h, r]
+//                          -> float32 [T, H, splits, R] without the division, and each part's maximum and sum
+//   latent_output_kernel   one block a (tile of 8 tokens, head): the parts merged and divided, then
+//                          y[h Dv + j] = sigmoid(gate_h) * sum_r Wuv[h Dv + j, r] o'[h, r]
 // Rotation: dims elements, pair i at angle position * inv_freq[i]; pairs = 1: elements (2i, 2i + 1), pairs = 0:
 // elements (i, i + dims / 2); elements from dims on pass unchanged.
 #include "common.cuh"
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(LT_THREADS) latent_query_kernel(
     float acc[LT_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = 0.f;
+#pragma unroll 8
     for (int d = 0; d < D; ++d) {
       const float w = to_f32(wuk[((size_t)h * D + d) * R + r]);
 #pragma unroll
@@ -149,12 +151,15 @@ extern "C" int sx_latent_query(const void* q, const void* wuk, int H, int D, int
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// RI: elements of the weighted latent a lane owns (R <= 32 * RI)
+// RI: elements of the weighted latent a lane owns (R <= 32 * RI).  The grid's z axis splits the window's key tiles
+// among blocks (single-token steps of few sequences would otherwise fill a fraction of the SMs); every block writes its
+// weighted sum without the division, out [T, H, splits, R], and its maximum and sum of weights, ml [T, H, splits, 2];
+// the output kernel merges them.
 template <typename T, int RI>
 __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
     const float* __restrict__ qa, const T* __restrict__ k_pages, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int maxp, int H, int R, int Dr, float scale,
-    int window, float* __restrict__ out) {
+    int window, float* __restrict__ out, float* __restrict__ ml) {
   extern __shared__ float sm[];
   const int E = R + Dr, ES = E + 1;        // a staged row is padded by one float: lanes read different rows
   float* ks = sm;                          // LT_KEYS * ES
@@ -163,19 +168,24 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
   pdl_trigger();
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y * LT_HEADS + warp;
+  const int split = blockIdx.z, splits = gridDim.z;
   const bool live = h < H;
   const int pos = positions[t];
   const int* bt = block_table + (size_t)seq_of_token[t] * maxp;
   if (live)
     for (int i = lane; i < E; i += 32) qs[warp * E + i] = qa[((size_t)t * H + h) * E + i];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int tiles = (pos - lo) / LT_KEYS + 1;
+  const int per = (tiles + splits - 1) / splits;
+  const int j_begin = lo + split * per * LT_KEYS;
+  const int j_end = min(pos, lo + (split + 1) * per * LT_KEYS - 1);      // last key of this block
   float m = -INFINITY, l = 0.f;
   float acc[RI];
 #pragma unroll
   for (int i = 0; i < RI; ++i) acc[i] = 0.f;
   const float* qh = qs + warp * E;
-  for (int j0 = lo; j0 <= pos; j0 += LT_KEYS) {
-    const int nk = min(LT_KEYS, pos - j0 + 1);
+  for (int j0 = j_begin; j0 <= j_end; j0 += LT_KEYS) {
+    const int nk = min(LT_KEYS, j_end - j0 + 1);
     __syncthreads();                        // the tile before is read out (and qs is written)
     for (int i = tid; i < nk * E; i += LT_HEADS * 32) {
       const int jj = i / E, e = i % E;
@@ -187,9 +197,16 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
     float s = -INFINITY;
     if (lane < nk) {
       const float* kr = ks + lane * ES;
-      float d = 0.f;
-      for (int e = 0; e < E; ++e) d = fmaf(qh[e], kr[e], d);
-      s = d * scale;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;      // four sums side by side: the chain of one would wait on itself
+      int e = 0;
+      for (; e + 3 < E; e += 4) {
+        d0 = fmaf(qh[e], kr[e], d0);
+        d1 = fmaf(qh[e + 1], kr[e + 1], d1);
+        d2 = fmaf(qh[e + 2], kr[e + 2], d2);
+        d3 = fmaf(qh[e + 3], kr[e + 3], d3);
+      }
+      for (; e < E; ++e) d0 = fmaf(qh[e], kr[e], d0);
+      s = ((d0 + d1) + (d2 + d3)) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = lane < nk ? expf(s - m_new) : 0.f;
@@ -209,11 +226,15 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
     }
   }
   if (live) {
-    const float inv = 1.f / l;
+    float* o = out + (((size_t)t * H + h) * splits + split) * R;
 #pragma unroll
     for (int i = 0; i < RI; ++i) {
       const int r = lane + 32 * i;
-      if (r < R) out[((size_t)t * H + h) * R + r] = acc[i] * inv;
+      if (r < R) o[r] = acc[i];
+    }
+    if (lane == 0) {
+      ml[(((size_t)t * H + h) * splits + split) * 2] = m;
+      ml[(((size_t)t * H + h) * splits + split) * 2 + 1] = l;
     }
   }
 }
@@ -221,23 +242,24 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
 template <typename T, int RI>
 static int latent_attn_launch(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
                               const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out,
-                              int T_, cudaStream_t stream) {
+                              float* ml, int splits, int T_, cudaStream_t stream) {
   const size_t smem = (size_t)(LT_KEYS * (R + Dr + 1) + LT_HEADS * (R + Dr)) * sizeof(float);
   if (smem > 200 * 1024) return SX_ERR_SIZE;
   if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<T, RI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  dim3 grid(T_, (H + LT_HEADS - 1) / LT_HEADS);
+  dim3 grid(T_, (H + LT_HEADS - 1) / LT_HEADS, splits);
   return sx_launch(latent_attn_kernel<T, RI>, grid, dim3(LT_HEADS * 32), smem, stream, qa, (const T*)k_pages, positions, seq_of_token,
-                   block_table, maxp, H, R, Dr, scale, window, out);
+                   block_table, maxp, H, R, Dr, scale, window, out, ml);
 }
 
 template <typename T>
 static int latent_attn_any(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
-                           const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out, int T_,
-                           cudaStream_t stream) {
-#define LT_CASE(RI) return latent_attn_launch<T, RI>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, T_, stream)
+                           const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out, float* ml,
+                           int splits, int T_, cudaStream_t stream) {
+#define LT_CASE(RI) return latent_attn_launch<T, RI>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, ml, splits, T_, stream)
   if (R <= 32 * 2) LT_CASE(2);
   if (R <= 32 * 4) LT_CASE(4);
   if (R <= 32 * 8) LT_CASE(8);
+  if (R <= 32 * 12) LT_CASE(12);
   if (R <= 32 * 16) LT_CASE(16);
   if (R <= 32 * 32) LT_CASE(32);
 #undef LT_CASE
@@ -246,63 +268,92 @@ static int latent_attn_any(const float* qa, const void* k_pages, const int* posi
 
 extern "C" int sx_latent_attention(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
                                    const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out,
-                                   int T, int dt, cudaStream_t stream) {
+                                   float* ml, int splits, int T, int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H <= 0 || R <= 0 || Dr < 0 || (H + LT_HEADS - 1) / LT_HEADS > 65535) return SX_ERR_SIZE;
-  if (dt == SX_F32) return latent_attn_any<float>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, T, stream);
-  if (dt == SX_BF16) return latent_attn_any<bf16>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, T, stream);
+  if (H <= 0 || R <= 0 || Dr < 0 || (H + LT_HEADS - 1) / LT_HEADS > 65535 || splits < 1 || splits > 64) return SX_ERR_SIZE;
+  if (dt == SX_F32) return latent_attn_any<float>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, ml, splits, T, stream);
+  if (dt == SX_BF16) return latent_attn_any<bf16>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, ml, splits, T, stream);
   return SX_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+#define LT_OUTS 4            // outputs a warp of the output kernel computes side by side
+
 template <typename T>
 __global__ void __launch_bounds__(LT_THREADS) latent_output_kernel(
-    const float* __restrict__ ol, const T* __restrict__ wuv, int H, int Dv, int R, const T* __restrict__ proj, int row,
-    int col_g, T* __restrict__ y, int n_tokens) {
+    const float* __restrict__ ol, const float* __restrict__ ml, int splits, const T* __restrict__ wuv, int H, int Dv, int R,
+    const T* __restrict__ proj, int row, int col_g, T* __restrict__ y, int n_tokens) {
   extern __shared__ float os[];          // LT_TOKENS * R
+  __shared__ float wsp[LT_TOKENS][64];   // each split's weight exp(m_s - M) / L
   pdl_wait();
   pdl_trigger();
   const int t0 = blockIdx.x * LT_TOKENS, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nt = min(LT_TOKENS, n_tokens - t0);
-  for (int i = tid; i < LT_TOKENS * R; i += LT_THREADS) {
-    const int tt = i / R, r = i % R;
-    os[i] = tt < nt ? ol[((size_t)(t0 + tt) * H + h) * R + r] : 0.f;
+  if (tid < LT_TOKENS) {
+    const int tt = tid;
+    if (tt < nt) {
+      const float* p = ml + ((size_t)(t0 + tt) * H + h) * splits * 2;
+      float M = -INFINITY, L = 0.f;
+      for (int s = 0; s < splits; ++s) M = fmaxf(M, p[2 * s]);
+      for (int s = 0; s < splits; ++s) L += p[2 * s + 1] * (p[2 * s] == -INFINITY ? 0.f : expf(p[2 * s] - M));
+      for (int s = 0; s < splits; ++s) wsp[tt][s] = (p[2 * s] == -INFINITY ? 0.f : expf(p[2 * s] - M)) / L;
+    }
   }
   __syncthreads();
-  for (int j = warp; j < Dv; j += LT_THREADS / 32) {
-    float acc[LT_TOKENS];
-#pragma unroll
-    for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = 0.f;
-    const T* wr = wuv + ((size_t)h * Dv + j) * R;
-    for (int r = lane; r < R; r += 32) {
-      const float w = to_f32(wr[r]);
-#pragma unroll
-      for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = fmaf(os[tt * R + r], w, acc[tt]);
+  for (int i = tid; i < LT_TOKENS * R; i += LT_THREADS) {
+    const int tt = i / R, r = i % R;
+    float v = 0.f;
+    if (tt < nt) {
+      const float* p = ol + ((size_t)(t0 + tt) * H + h) * splits * R + r;
+      for (int s = 0; s < splits; ++s) v = fmaf(wsp[tt][s], p[(size_t)s * R], v);
     }
+    os[i] = v;
+  }
+  __syncthreads();
+  for (int j0 = warp * LT_OUTS; j0 < Dv; j0 += (LT_THREADS / 32) * LT_OUTS) {
+    float acc[LT_OUTS][LT_TOKENS];
 #pragma unroll
-    for (int tt = 0; tt < LT_TOKENS; ++tt) {
-      const float s = warp_sum(acc[tt]);
-      if (lane == 0 && tt < nt) {
-        float g = 1.f;
-        if (col_g >= 0) g = 1.f / (1.f + expf(-to_f32(proj[(size_t)(t0 + tt) * row + col_g + h])));
-        y[(size_t)(t0 + tt) * H * Dv + h * Dv + j] = from_f32<T>(s * g);
+    for (int a = 0; a < LT_OUTS; ++a)
+#pragma unroll
+      for (int tt = 0; tt < LT_TOKENS; ++tt) acc[a][tt] = 0.f;
+#pragma unroll 2
+    for (int r = lane; r < R; r += 32) {
+      float w[LT_OUTS];
+#pragma unroll
+      for (int a = 0; a < LT_OUTS; ++a) w[a] = j0 + a < Dv ? to_f32(wuv[((size_t)h * Dv + j0 + a) * R + r]) : 0.f;
+#pragma unroll
+      for (int tt = 0; tt < LT_TOKENS; ++tt) {
+        const float x = os[tt * R + r];
+#pragma unroll
+        for (int a = 0; a < LT_OUTS; ++a) acc[a][tt] = fmaf(x, w[a], acc[a][tt]);
       }
     }
+#pragma unroll
+    for (int a = 0; a < LT_OUTS; ++a)
+#pragma unroll
+      for (int tt = 0; tt < LT_TOKENS; ++tt) {
+        const float s = warp_sum(acc[a][tt]);
+        if (lane == 0 && tt < nt && j0 + a < Dv) {
+          float g = 1.f;
+          if (col_g >= 0) g = 1.f / (1.f + expf(-to_f32(proj[(size_t)(t0 + tt) * row + col_g + h])));
+          y[(size_t)(t0 + tt) * H * Dv + h * Dv + j0 + a] = from_f32<T>(s * g);
+        }
+      }
   }
 }
 
-extern "C" int sx_latent_output(const float* ol, const void* wuv, int H, int Dv, int R, const void* proj, int row, int col_g,
-                                void* y, int T, int dt, cudaStream_t stream) {
+extern "C" int sx_latent_output(const float* ol, const float* ml, int splits, const void* wuv, int H, int Dv, int R,
+                                const void* proj, int row, int col_g, void* y, int T, int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H <= 0 || H > 65535 || Dv <= 0 || R <= 0) return SX_ERR_SIZE;
+  if (H <= 0 || H > 65535 || Dv <= 0 || R <= 0 || splits < 1 || splits > 64) return SX_ERR_SIZE;
   const size_t smem = (size_t)LT_TOKENS * R * sizeof(float);
   if (smem > 48 * 1024) return SX_ERR_SIZE;
   dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H);
   if (dt == SX_F32)
-    return sx_launch(latent_output_kernel<float>, grid, dim3(LT_THREADS), smem, stream, ol, (const float*)wuv, H, Dv, R,
+    return sx_launch(latent_output_kernel<float>, grid, dim3(LT_THREADS), smem, stream, ol, ml, splits, (const float*)wuv, H, Dv, R,
                      (const float*)proj, row, col_g, (float*)y, T);
   if (dt == SX_BF16)
-    return sx_launch(latent_output_kernel<bf16>, grid, dim3(LT_THREADS), smem, stream, ol, (const bf16*)wuv, H, Dv, R,
+    return sx_launch(latent_output_kernel<bf16>, grid, dim3(LT_THREADS), smem, stream, ol, ml, splits, (const bf16*)wuv, H, Dv, R,
                      (const bf16*)proj, row, col_g, (bf16*)y, T);
   return SX_ERR_DTYPE;
 }

@@ -33,7 +33,17 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x,
   for (int e = warp; e < E; e += 4) {
     const float* w = wr + (size_t)e * W;
     float d = 0.f;
-    for (int i = lane; i < W; i += 32) d = fmaf(xs[i], w[i], d);
+    if ((W & 3) == 0 && ((uintptr_t)wr & 15) == 0) {          // 16 bytes a load, four loads on the way
+      float d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 4
+      for (int i = lane * 4; i < W; i += 128) {
+        const float4 w4 = *reinterpret_cast<const float4*>(w + i);
+        d = fmaf(xs[i], w4.x, d); d1 = fmaf(xs[i + 1], w4.y, d1); d2 = fmaf(xs[i + 2], w4.z, d2); d3 = fmaf(xs[i + 3], w4.w, d3);
+      }
+      d = (d + d1) + (d2 + d3);
+    } else {
+      for (int i = lane; i < W; i += 32) d = fmaf(xs[i], w[i], d);
+    }
     d = warp_sum(d);
     if (lane == 0) z[e] = d;
   }

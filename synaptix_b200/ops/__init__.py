@@ -41,7 +41,8 @@ __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavail
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
                    "attn_tc": ("the tcgen05 prompt attention (attn_tc)", "attn_tc_status"),
                    "attn_decode": ("the TMA-fed decode attention (attn_decode)", "attn_decode_status"),
-                   "gemm_ws": ("the weight-streaming tcgen05 product (gemm_ws)", "gemm_ws_status")}
+                   "gemm_ws": ("the weight-streaming tcgen05 product (gemm_ws)", "gemm_ws_status"),
+                   "moe_tc": ("the experts' grouped tcgen05 product (moe_tc)", "moe_tc_status")}
 
 
 def check_status(readers=None) -> None:
@@ -56,7 +57,8 @@ def check_status(readers=None) -> None:
         from .attention import attn_decode_status, attn_tc_status
         from .gemm_tc import gemm_tc_status
         from .gemm_ws import gemm_ws_status
-        fns = {"gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status, "attn_decode_status": attn_decode_status,
+        from .moe import moe_tc_status
+        fns = {"moe_tc_status": moe_tc_status, "gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status, "attn_decode_status": attn_decode_status,
                "gemm_ws_status": gemm_ws_status}
         readers = {}
         for lib, (what, fname) in _STATUS_READERS.items():

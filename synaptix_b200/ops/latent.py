@@ -51,38 +51,74 @@ def latent_query(q: torch.Tensor, wuk: torch.Tensor, heads: int, dim: int, rot_d
     return qa
 
 
+class WeightedLatents:
+    """What ``latent_attention`` leaves: per (token, head) and part of the window the weighted sum of ``c`` without its
+    division, ``parts`` float32 ``[T, heads, splits, kv_rank]``, and each part's maximum and sum of weights, ``ml``
+    float32 ``[T, heads, splits, 2]``; ``latent_output`` merges them."""
+    __slots__ = ("parts", "ml", "splits")
+
+    def __init__(self, parts, ml, splits):
+        self.parts, self.ml, self.splits = parts, ml, splits
+
+    def merged(self) -> torch.Tensor:
+        """float32 ``[T, heads, kv_rank]`` (for tests: torch arithmetic)."""
+        m, l = self.ml[..., 0], self.ml[..., 1]
+        w = torch.exp(m - m.max(dim=-1, keepdim=True).values)
+        return (self.parts * w[..., None]).sum(2) / (l * w).sum(-1, keepdim=True)
+
+
+_SMS = {}
+
+
+def _pick_latent_splits(ctx, heads: int, window: Optional[int], device) -> int:
+    """Parts of the window for single-token steps, so that the blocks fill the SMs about twice; prompts take one."""
+    if not ctx.all_single:
+        return 1
+    keys = ctx.max_len if window is None else min(ctx.max_len, int(window))
+    tiles = (keys + 31) // 32
+    idx = device.index or 0
+    if idx not in _SMS:
+        _SMS[idx] = torch.cuda.get_device_properties(device).multi_processor_count
+    blocks = ctx.n_tokens * ((heads + 7) // 8)
+    want = (2 * _SMS[idx] + blocks - 1) // blocks
+    return max(1, min(want, tiles // 2, 16))
+
+
 def latent_attention(qa: torch.Tensor, k_pages: torch.Tensor, ctx, block_table: torch.Tensor, heads: int, kv_rank: int,
-                     rot_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
+                     rot_dim: int, scale: float, window: Optional[int], splits: Optional[int] = None) -> WeightedLatents:
     """Causal (optionally windowed) softmax attention of ``qa`` float32 ``[T, heads, kv_rank + rot_dim]`` over the cache
-    rows ``[c | k_rot]``; the weights are applied to ``c``: float32 ``[T, heads, kv_rank]``."""
+    rows ``[c | k_rot]``; the weights are applied to ``c`` (see ``WeightedLatents``)."""
     require_cuda(qa, k_pages, block_table)
     T = qa.shape[0]
     if qa.dtype != torch.float32 or tuple(qa.shape[1:]) != (heads, kv_rank + rot_dim):
         raise KernelError("latent_attention: queries are float32 [T, heads, kv_rank + rot_dim]")
     if k_pages.dim() != 4 or tuple(k_pages.shape[1:]) != (1, 64, kv_rank + rot_dim):
         raise KernelError("latent_attention: cache pages must be [n_pages, 1, 64, kv_rank + rot_dim]")
-    out = torch.empty((T, heads, kv_rank), dtype=torch.float32, device=qa.device)
+    if splits is None:
+        splits = _pick_latent_splits(ctx, heads, window, qa.device)
+    out = torch.empty((T, heads, splits, kv_rank), dtype=torch.float32, device=qa.device)
+    ml = torch.empty((T, heads, splits, 2), dtype=torch.float32, device=qa.device)
     check(fn("latent", "sx_latent_attention")(ptr(qa), ptr(k_pages), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(block_table),
                                               c_int(block_table.shape[1]), c_int(heads), c_int(kv_rank), c_int(rot_dim),
-                                              c_float(scale), c_int(0 if window is None else int(window)), ptr(out), c_int(T),
-                                              c_int(dt_code(k_pages.dtype)), stream()), "latent_attention")
-    return out
+                                              c_float(scale), c_int(0 if window is None else int(window)), ptr(out), ptr(ml),
+                                              c_int(splits), c_int(T), c_int(dt_code(k_pages.dtype)), stream()), "latent_attention")
+    return WeightedLatents(out, ml, splits)
 
 
-def latent_output(ol: torch.Tensor, wuv: torch.Tensor, heads: int, vdim: int, kv_rank: int, proj: torch.Tensor, col_gate: int,
+def latent_output(ol: WeightedLatents, wuv: torch.Tensor, heads: int, vdim: int, kv_rank: int, proj: torch.Tensor, col_gate: int,
                   out_dtype: torch.dtype) -> torch.Tensor:
-    """``y[t, h * vdim + j] = sigmoid(proj[t, col_gate + h]) * sum_r wuv[h * vdim + j, r] * ol[t, h, r]`` (no gate if
-    ``col_gate < 0``); ``[T, heads * vdim]`` in ``out_dtype``."""
-    require_cuda(ol, wuv, proj)
-    T = ol.shape[0]
-    if ol.dtype != torch.float32 or tuple(ol.shape[1:]) != (heads, kv_rank) or tuple(wuv.shape) != (heads * vdim, kv_rank):
+    """``y[t, h * vdim + j] = sigmoid(proj[t, col_gate + h]) * sum_r wuv[h * vdim + j, r] * o[t, h, r]`` with ``o`` the
+    merged, divided weighted latents (no gate if ``col_gate < 0``); ``[T, heads * vdim]`` in ``out_dtype``."""
+    require_cuda(ol.parts, ol.ml, wuv, proj)
+    T = ol.parts.shape[0]
+    if tuple(ol.parts.shape[1:]) != (heads, ol.splits, kv_rank) or tuple(wuv.shape) != (heads * vdim, kv_rank):
         raise KernelError("latent_output: sizes do not fit")
     if wuv.dtype != out_dtype or proj.dtype != out_dtype or (col_gate >= 0 and col_gate + heads > proj.shape[1]):
         raise KernelError("latent_output: dtypes or the gate's columns do not fit")
-    y = torch.empty((T, heads * vdim), dtype=out_dtype, device=ol.device)
-    check(fn("latent", "sx_latent_output")(ptr(ol), ptr(wuv), c_int(heads), c_int(vdim), c_int(kv_rank), ptr(proj),
-                                           c_int(proj.shape[1]), c_int(col_gate), ptr(y), c_int(T), c_int(dt_code(out_dtype)),
-                                           stream()), "latent_output")
+    y = torch.empty((T, heads * vdim), dtype=out_dtype, device=wuv.device)
+    check(fn("latent", "sx_latent_output")(ptr(ol.parts), ptr(ol.ml), c_int(ol.splits), ptr(wuv), c_int(heads), c_int(vdim),
+                                           c_int(kv_rank), ptr(proj), c_int(proj.shape[1]), c_int(col_gate), ptr(y), c_int(T),
+                                           c_int(dt_code(out_dtype)), stream()), "latent_output")
     return y
 
 

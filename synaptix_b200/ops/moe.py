@@ -5,7 +5,24 @@ from typing import NamedTuple
 
 import torch
 
+import ctypes
+
 from ._lib import KernelError, c_float, c_int, check, dt_code, fn, ptr, require_cuda, stream
+
+# From this many (token, choice) rows on, bfloat16 products run the tcgen05 kernel (128-row tiles, rows gathered into
+# sorted order first); fewer rows (single-token steps, short prompts) run the mma.sync kernel, which gathers as it loads.
+TC_MIN_ROWS = 512
+
+
+def _tc_fits(rows: int, K: int, dtype) -> bool:
+    return dtype == torch.bfloat16 and rows >= TC_MIN_ROWS and K % 8 == 0
+
+
+def moe_tc_status(reset: bool = False) -> int:
+    """0, or which bounded wait of the tcgen05 grouped product ran out (1 producer, 2 MMA issuer, 3 epilogue)."""
+    v = ctypes.c_int(0)
+    check(fn("moe_tc", "sx_moe_tc_status")(ctypes.byref(v), c_int(1 if reset else 0)), "moe_tc_status", launches=0)
+    return int(v.value)
 
 
 class ExpertPlan(NamedTuple):
@@ -53,6 +70,12 @@ def moe_gate_up(x: torch.Tensor, gate_up: torch.Tensor, plan: ExpertPlan, top: i
         raise KernelError("moe_gate_up: sizes or dtypes do not fit")
     rows = plan.order.numel()
     z = torch.empty((rows, ff2 // 2), dtype=x.dtype, device=x.device)
+    if _tc_fits(rows, W, x.dtype):
+        xs = torch.empty((rows, W), dtype=x.dtype, device=x.device)
+        check(fn("moe_tc", "sx_moe_gather")(ptr(x), ptr(plan.order), ptr(xs), c_int(rows), c_int(W), c_int(top), stream()), "moe_gather")
+        check(fn("moe_tc", "sx_moe_tc")(ptr(xs), ptr(gate_up), ptr(z), ptr(plan.offsets), c_int(rows), c_int(E), c_int(ff2 // 2),
+                                        c_int(W), c_int(1), stream()), "moe_gate_up")
+        return z
     check(fn("moe", "sx_moe_gemm")(ptr(x), ptr(gate_up), ptr(z), ptr(plan.offsets), ptr(plan.order), c_int(rows), c_int(E),
                                    c_int(ff2 // 2), c_int(W), c_int(top), c_int(1), c_int(dt_code(x.dtype)),
                                    c_int(dt_code(z.dtype)), stream()), "moe_gate_up")
@@ -67,6 +90,10 @@ def moe_down(z: torch.Tensor, down: torch.Tensor, plan: ExpertPlan) -> torch.Ten
     if ff2 != ff or E != plan.experts or down.dtype != z.dtype or rows != plan.order.numel():
         raise KernelError("moe_down: sizes or dtypes do not fit")
     y = torch.empty((rows, W), dtype=torch.float32, device=z.device)
+    if _tc_fits(rows, ff, z.dtype):
+        check(fn("moe_tc", "sx_moe_tc")(ptr(z), ptr(down), ptr(y), ptr(plan.offsets), c_int(rows), c_int(E), c_int(W), c_int(ff),
+                                        c_int(0), stream()), "moe_down")
+        return y
     check(fn("moe", "sx_moe_gemm")(ptr(z), ptr(down), ptr(y), ptr(plan.offsets), ptr(plan.order), c_int(rows), c_int(E),
                                    c_int(W), c_int(ff), c_int(1), c_int(0), c_int(dt_code(z.dtype)), c_int(dt_code(y.dtype)),
                                    stream()), "moe_down")

@@ -198,14 +198,15 @@ def test_latent_attention_sees_the_windows_edge_and_a_key_far_back(heads, R, Dr,
     bt = i32([table])
     tol = dict(atol=2e-5, rtol=2e-5) if dtype == "float32" else dict(atol=2e-3, rtol=2e-3)
     ctx = step_ctx([0], [n], [0], tables=[bt])                  # the whole prompt
-    got = ops.latent_attention(qa.cuda(), pages, ctx, bt, heads, R, Dr, scale, window).cpu().double()
+    got = ops.latent_attention(qa.cuda(), pages, ctx, bt, heads, R, Dr, scale, window).merged().cpu().double()
     assert torch.allclose(got, ref, **tol), float((got - ref).abs().max())
     standout = [p for p, j in probes.items() if 0 <= p - j < w and p != j]
     assert (standout or w == 1) and all(float((ref[p] - rows[probes[p], :R]).abs().max()) < 0.05 for p in standout)
     for p in probes:                                            # single queries behind p cached tokens
         ctx = step_ctx([p], [1], [0], tables=[bt])
-        got = ops.latent_attention(qa[p:p + 1].cuda(), pages, ctx, bt, heads, R, Dr, scale, window).cpu().double()
-        assert torch.allclose(got, ref[p:p + 1], **tol), p
+        for splits in (None, 1, 3, 16):                         # the window in parts, merged (more parts than key tiles too)
+            got = ops.latent_attention(qa[p:p + 1].cuda(), pages, ctx, bt, heads, R, Dr, scale, window, splits=splits)
+            assert torch.allclose(got.merged().cpu().double(), ref[p:p + 1], **tol), (p, splits)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -257,7 +258,7 @@ def test_latent_attention_layer_against_per_head_keys_and_values(dtype, pairs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,experts,top,ff,width", [(1, 5, 2, 24, 52), (3, 1, 1, 16, 40), (70, 7, 7, 40, 64), (300, 16, 4, 100, 130), (9, 12, 3, 64, 320), (400, 6, 2, 136, 264)])
+@pytest.mark.parametrize("T,experts,top,ff,width", [(1, 5, 2, 24, 52), (3, 1, 1, 16, 40), (70, 7, 7, 40, 64), (300, 16, 4, 100, 130), (9, 12, 3, 64, 320), (400, 6, 2, 136, 264), (700, 5, 3, 200, 328)])
 def test_mixture_of_experts(T, experts, top, ff, width, dtype):
     """Router, sort by expert, grouped products and the weighted sum against the plain form; one token's input is made
     to fall on a near tie of the router, which the comparison leaves out."""
@@ -330,7 +331,7 @@ def test_whole_prompts_every_place(engines, name, dtype):
 
 def test_whole_prompts_in_bfloat16_take_the_per_head_form(engines, monkeypatch):
     """Head sizes a tensor-core attention kernel takes: a whole prompt of 256 tokens and more goes through per-head keys
-    and values in pages of the step's own (two of the three attention layers of this model), a shorter one, a portion
+    and values in pages of the step's own (all three attention layers of this model), a shorter one, a portion
     behind cached tokens and single tokens through the latent form; all agree with the plain implementation."""
     from synaptix_b200 import ops
     from synaptix_b200.engine import Entry
@@ -342,11 +343,11 @@ def test_whole_prompts_in_bfloat16_take_the_per_head_form(engines, monkeypatch):
     ref = oracle_logits("PT", tuple(toks))
     s = eng.open()
     got = [eng.step([Entry(s, toks[:300], list(range(300)))])]
-    assert len(calls) == 2
+    n_first = len(calls)
     got.append(eng.step([Entry(s, toks[300:399], list(range(99)))]))
     got.append(eng.step([Entry(s, toks[399:], [0])]))
-    assert len(calls) == 2
     eng.close(s)
+    assert n_first == 3 and len(calls) == 3
     assert_close(torch.cat(got), ref, "bfloat16", "PT: per-head form, then the latent form")
 
 
