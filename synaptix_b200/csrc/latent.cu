@@ -23,6 +23,7 @@
 #include <math.h>
 
 #define LT_THREADS 256
+#define LT_QTHREADS 128       // threads of a block of the query kernel
 #define LT_TOKENS 8          // tokens a block of the query / output kernels
 #define LT_HEADS 8           // heads (warps) a block of the attention kernel
 #define LT_KEYS 32           // keys staged at a time
@@ -86,7 +87,7 @@ extern "C" int sx_latent_prepare(const void* proj, int row, int Rq, int col, int
 
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(LT_THREADS) latent_query_kernel(
+__global__ void __launch_bounds__(LT_QTHREADS) latent_query_kernel(
     const T* __restrict__ q, const T* __restrict__ wuk, int H, int D, int Dr, int R, const float* __restrict__ inv_freq,
     int dims, int pairs, const int* __restrict__ positions, float* __restrict__ qa, int n_tokens) {
   extern __shared__ float qs[];          // LT_TOKENS * D
@@ -95,12 +96,13 @@ __global__ void __launch_bounds__(LT_THREADS) latent_query_kernel(
   const int t0 = blockIdx.x * LT_TOKENS, h = blockIdx.y, tid = threadIdx.x;
   const int nt = min(LT_TOKENS, n_tokens - t0);
   const int QW = H * (D + Dr);
-  for (int i = tid; i < LT_TOKENS * D; i += LT_THREADS) {
+  for (int i = tid; i < LT_TOKENS * D; i += LT_QTHREADS) {
     const int tt = i / D, d = i % D;
     qs[i] = tt < nt ? to_f32(q[(size_t)(t0 + tt) * QW + h * (D + Dr) + d]) : 0.f;
   }
   __syncthreads();
-  for (int r = tid; r < R; r += LT_THREADS) {
+  // the grid's z axis shares the latent's elements: LT_QTHREADS a block
+  for (int r = blockIdx.z * LT_QTHREADS + tid; r < min(R, (int)(blockIdx.z + 1) * LT_QTHREADS); r += LT_QTHREADS) {
     float acc[LT_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = 0.f;
@@ -114,8 +116,9 @@ __global__ void __launch_bounds__(LT_THREADS) latent_query_kernel(
     for (int tt = 0; tt < LT_TOKENS; ++tt)
       if (tt < nt) qa[((size_t)(t0 + tt) * H + h) * (R + Dr) + r] = acc[tt];
   }
+  if (blockIdx.z != 0) return;
   // the rotated part
-  for (int i = tid; i < nt * (dims / 2); i += LT_THREADS) {
+  for (int i = tid; i < nt * (dims / 2); i += LT_QTHREADS) {
     const int tt = i / (dims / 2), p = i % (dims / 2);
     int ia, ib;
     rot_pair_index(p, dims, pairs, ia, ib);
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(LT_THREADS) latent_query_kernel(
     o[ib] = v * cs + u * sn;
   }
   const int rest = Dr - dims;
-  for (int i = tid; i < nt * rest; i += LT_THREADS) {
+  for (int i = tid; i < nt * rest; i += LT_QTHREADS) {
     const int tt = i / rest, j = dims + i % rest;
     qa[((size_t)(t0 + tt) * H + h) * (R + Dr) + R + j] = to_f32(q[(size_t)(t0 + tt) * QW + h * (D + Dr) + D + j]);
   }
@@ -140,12 +143,12 @@ extern "C" int sx_latent_query(const void* q, const void* wuk, int H, int D, int
   if (H <= 0 || H > 65535 || D < 0 || R <= 0 || dims < 0 || dims > Dr || (dims & 1)) return SX_ERR_SIZE;
   const size_t smem = (size_t)LT_TOKENS * (D > 0 ? D : 1) * sizeof(float);
   if (smem > 48 * 1024) return SX_ERR_SIZE;
-  dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H);
+  dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H, (R + LT_QTHREADS - 1) / LT_QTHREADS);
   if (dt == SX_F32)
-    return sx_launch(latent_query_kernel<float>, grid, dim3(LT_THREADS), smem, stream, (const float*)q, (const float*)wuk, H, D, Dr,
+    return sx_launch(latent_query_kernel<float>, grid, dim3(LT_QTHREADS), smem, stream, (const float*)q, (const float*)wuk, H, D, Dr,
                      R, inv_freq, dims, pairs, positions, qa, T);
   if (dt == SX_BF16)
-    return sx_launch(latent_query_kernel<bf16>, grid, dim3(LT_THREADS), smem, stream, (const bf16*)q, (const bf16*)wuk, H, D, Dr,
+    return sx_launch(latent_query_kernel<bf16>, grid, dim3(LT_QTHREADS), smem, stream, (const bf16*)q, (const bf16*)wuk, H, D, Dr,
                      R, inv_freq, dims, pairs, positions, qa, T);
   return SX_ERR_DTYPE;
 }
@@ -187,10 +190,26 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
   for (int j0 = j_begin; j0 <= j_end; j0 += LT_KEYS) {
     const int nk = min(LT_KEYS, j_end - j0 + 1);
     __syncthreads();                        // the tile before is read out (and qs is written)
-    for (int i = tid; i < nk * E; i += LT_HEADS * 32) {
-      const int jj = i / E, e = i % E;
-      const int j = j0 + jj;
-      ks[jj * ES + e] = to_f32(k_pages[((size_t)bt[j >> 6] * SX_PAGE + (j & 63)) * E + e]);
+    constexpr int VEC = 16 / (int)sizeof(T);
+    if (E % VEC == 0) {
+      // a warp takes whole rows: the page is looked up once a row and the lanes copy 16 bytes each
+      for (int jj = warp; jj < nk; jj += LT_HEADS) {
+        const int j = j0 + jj;
+        const uint4* src = reinterpret_cast<const uint4*>(k_pages + ((size_t)bt[j >> 6] * SX_PAGE + (j & 63)) * E);
+        float* dst = ks + jj * ES;
+        for (int c = lane; c < E / VEC; c += 32) {
+          const uint4 v = src[c];
+          const T* x = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) dst[c * VEC + i] = to_f32(x[i]);
+        }
+      }
+    } else {
+      for (int i = tid; i < nk * E; i += LT_HEADS * 32) {
+        const int jj = i / E, e = i % E;
+        const int j = j0 + jj;
+        ks[jj * ES + e] = to_f32(k_pages[((size_t)bt[j >> 6] * SX_PAGE + (j & 63)) * E + e]);
+      }
     }
     __syncthreads();
     if (!live) continue;
@@ -310,7 +329,9 @@ __global__ void __launch_bounds__(LT_THREADS) latent_output_kernel(
     os[i] = v;
   }
   __syncthreads();
-  for (int j0 = warp * LT_OUTS; j0 < Dv; j0 += (LT_THREADS / 32) * LT_OUTS) {
+  // the grid's z axis shares the head's outputs: 32 a block
+  const int j_hi = min(Dv, (int)(blockIdx.z + 1) * (LT_THREADS / 32) * LT_OUTS);
+  for (int j0 = blockIdx.z * (LT_THREADS / 32) * LT_OUTS + warp * LT_OUTS; j0 < j_hi; j0 += (LT_THREADS / 32) * LT_OUTS) {
     float acc[LT_OUTS][LT_TOKENS];
 #pragma unroll
     for (int a = 0; a < LT_OUTS; ++a)
@@ -348,7 +369,7 @@ extern "C" int sx_latent_output(const float* ol, const float* ml, int splits, co
   if (H <= 0 || H > 65535 || Dv <= 0 || R <= 0 || splits < 1 || splits > 64) return SX_ERR_SIZE;
   const size_t smem = (size_t)LT_TOKENS * R * sizeof(float);
   if (smem > 48 * 1024) return SX_ERR_SIZE;
-  dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H);
+  dim3 grid((T + LT_TOKENS - 1) / LT_TOKENS, H, (Dv + (LT_THREADS / 32) * LT_OUTS - 1) / ((LT_THREADS / 32) * LT_OUTS));
   if (dt == SX_F32)
     return sx_launch(latent_output_kernel<float>, grid, dim3(LT_THREADS), smem, stream, ol, ml, splits, (const float*)wuv, H, Dv, R,
                      (const float*)proj, row, col_g, (float*)y, T);

@@ -12,12 +12,12 @@
 //   mlstm_walk_kernel   one block a (head, sequence) walks the tokens one after the other with S in shared memory
 //                       (single-token steps, short portions, and sizes the pieces do not take).
 //   pieces of 64 tokens (long portions):
-//   mlstm_gates_kernel  a block a (head, sequence): the gates of all tokens, the running sums b of f inside each piece,
-//                       each piece's own maximum m_loc = max_j (b_end - b_j + i_j), and then, one after the other
-//                       over the pieces, the maximum m at every piece's begin (m_end = max(b_end + m_begin, m_loc)).
+//   mlstm_gates_kernel  a block a (piece, head, sequence): the gates of its tokens, the running sums b of f inside the
+//                       piece and the piece's own maximum m_loc = max_j (b_end - b_j + i_j).
 //   mlstm_piece_kernel  a block a (piece, head, sequence): U = sum_j exp(b_end - b_j + i_j - m_loc) k_j v_j^T and the
 //                       same sum of k_j alone.
-//   mlstm_carry_kernel  a block a (head, sequence) and slice of the state: the state at every piece's begin,
+//   mlstm_carry_kernel  a block a (head, sequence) and slice of the state: the maximum at every piece's begin
+//                       (m_end = max(b_end + m_begin, m_loc)) and the state there,
 //                       S_end = exp(b_end + m_begin - m_end) S_begin + exp(m_loc - m_end) U, one piece after the other;
 //                       the last one is the sequence's new state.
 //   mlstm_apply_kernel  a block a (piece, head, sequence): with m_i = max(b_i + m_begin, max_{j<=i} (b_i - b_j + i_j)),
@@ -153,44 +153,36 @@ struct MlPieces {
   int P;
 };
 
+// a block a (piece, head, sequence): the piece's gates, running sums and own maximum (info[0], info[1])
 __global__ void __launch_bounds__(ML_PIECE) mlstm_gates_kernel(MlArgs a, MlPieces w) {
   __shared__ float gf[ML_PIECE], av[ML_PIECE];
   pdl_wait();
   pdl_trigger();
-  const int h = blockIdx.x, s = blockIdx.y, j = threadIdx.x, H = a.H;
-  const int t0 = a.cu_seqlens[s], len = a.cu_seqlens[s + 1] - t0;
-  float* mg = a.m + (size_t)a.seq_slots[s] * H + h;
-  float m = *mg;
-  for (int p = 0; p * ML_PIECE < len; ++p) {
-    const int L = min(ML_PIECE, len - p * ML_PIECE);
-    const int t = t0 + p * ML_PIECE + j;
-    float gi = 0.f;
-    if (j < L) {
-      gi = ml_cap(a.gates[(size_t)t * 2 * H + h] + a.bias[h], a.cap);
-      gf[j] = ml_logsigmoid(ml_cap(a.gates[(size_t)t * 2 * H + H + h] + a.bias[H + h], a.cap));
-    }
-    __syncthreads();
-    float b = 0.f;
-    if (j < L) {
-      for (int x = 0; x <= j; ++x) b += gf[x];
-      av[j] = gi - b;
-      w.tok[((size_t)t * H + h) * 2] = gi - b;
-      w.tok[((size_t)t * H + h) * 2 + 1] = b;
-    }
-    __syncthreads();
-    if (j == L - 1) {                    // b is b_end here
-      float mloc = -INFINITY;
-      for (int x = 0; x < L; ++x) mloc = fmaxf(mloc, b + av[x]);
-      const float mend = fmaxf(b + m, mloc);
-      float* o = w.info + (((size_t)s * w.P + p) * H + h) * 4;
-      o[0] = b; o[1] = mloc; o[2] = m; o[3] = mend;
-      gf[0] = mend;
-    }
-    __syncthreads();
-    m = gf[0];
-    __syncthreads();
+  const int p = blockIdx.x, h = blockIdx.y, s = blockIdx.z, j = threadIdx.x, H = a.H;
+  const int t0 = a.cu_seqlens[s] + p * ML_PIECE, len = a.cu_seqlens[s + 1] - t0;
+  if (len <= 0) return;
+  const int L = min(ML_PIECE, len);
+  const int t = t0 + j;
+  float gi = 0.f;
+  if (j < L) {
+    gi = ml_cap(a.gates[(size_t)t * 2 * H + h] + a.bias[h], a.cap);
+    gf[j] = ml_logsigmoid(ml_cap(a.gates[(size_t)t * 2 * H + H + h] + a.bias[H + h], a.cap));
   }
-  if (j == 0) *mg = m;
+  __syncthreads();
+  float b = 0.f;
+  if (j < L) {
+    for (int x = 0; x <= j; ++x) b += gf[x];
+    av[j] = gi - b;
+    w.tok[((size_t)t * H + h) * 2] = gi - b;
+    w.tok[((size_t)t * H + h) * 2 + 1] = b;
+  }
+  __syncthreads();
+  if (j == L - 1) {                    // b is b_end here
+    float mloc = -INFINITY;
+    for (int x = 0; x < L; ++x) mloc = fmaxf(mloc, b + av[x]);
+    float* o = w.info + (((size_t)s * w.P + p) * H + h) * 4;
+    o[0] = b; o[1] = mloc;
+  }
 }
 
 // U = sum_j w_j k_j v_j^T (D x Dv) and sum_j w_j k_j (D), w_j = exp(a_j + b_end - m_loc); 4 x 4 results a thread
@@ -260,6 +252,9 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_piece_kernel(MlArgs a, MlPie
   }
 }
 
+// every thread walks the pieces' maxima itself (m_end = max(b_end + m_begin, m_loc), a few numbers a piece) and one
+// thread a (head, sequence) leaves them for the apply kernel (info[2], info[3]); the sequence's new maximum is written
+// by the apply kernel, after every block here has read the old one
 __global__ void __launch_bounds__(ML_THREADS) mlstm_carry_kernel(MlArgs a, MlPieces w) {
   pdl_wait();
   pdl_trigger();
@@ -268,17 +263,34 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_carry_kernel(MlArgs a, MlPie
   const size_t e = (size_t)blockIdx.x * ML_THREADS + threadIdx.x;
   if (e >= n_el) return;
   const int len = a.cu_seqlens[s + 1] - a.cu_seqlens[s];
+  const int np = (len + ML_PIECE - 1) / ML_PIECE;
   const int slot = a.seq_slots[s];
   float* home = e < (size_t)a.D * a.Dv ? a.S + ((size_t)slot * H + h) * a.D * a.Dv + e
                                         : a.n + ((size_t)slot * H + h) * a.D + (e - (size_t)a.D * a.Dv);
   float S = *home;
-  for (int p = 0; p * ML_PIECE < len; ++p) {
-    const float* info = w.info + (((size_t)s * w.P + p) * H + h) * 4;
-    const float fa = expf(info[0] + info[2] - info[3]), fb = expf(info[1] - info[3]);
-    float* u = w.st + (((size_t)s * w.P + p) * H + h) * n_el + e;
-    const float own = *u;
-    *u = S;
-    S = fa * S + fb * own;
+  float m = a.m[(size_t)slot * H + h];
+  for (int p0 = 0; p0 < np; p0 += 8) {
+    float own[8], bend[8], mloc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (p0 + i < np) {                 // eight pieces' loads on the way before the chain below waits for any
+        const float* info = w.info + (((size_t)s * w.P + p0 + i) * H + h) * 4;
+        bend[i] = info[0]; mloc[i] = info[1];
+        own[i] = w.st[(((size_t)s * w.P + p0 + i) * H + h) * n_el + e];
+      }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (p0 + i < np) {
+        const float mend = fmaxf(bend[i] + m, mloc[i]);
+        const float fa = expf(bend[i] + m - mend), fb = expf(mloc[i] - mend);
+        if (e == 0) {
+          float* info = w.info + (((size_t)s * w.P + p0 + i) * H + h) * 4;
+          info[2] = m; info[3] = mend;
+        }
+        w.st[(((size_t)s * w.P + p0 + i) * H + h) * n_el + e] = S;
+        S = fa * S + fb * own[i];
+        m = mend;
+      }
   }
   *home = S;
 }
@@ -304,6 +316,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
   const int L = min(ML_PIECE, len);
   const float* info = w.info + (((size_t)s * w.P + p) * H + h) * 4;
   const float mbeg = info[2];
+  if (tid == 0 && len <= ML_PIECE) a.m[(size_t)a.seq_slots[s] * H + h] = info[3];     // the last piece: the new maximum
   const float* S0 = w.st + (((size_t)s * w.P + p) * H + h) * ((size_t)D * Dv + D);
   const float* n0 = S0 + (size_t)D * Dv;
   const T* proj = (const T*)a.proj;
@@ -335,6 +348,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int x = 0; x < 4; ++x) acc[i][x] = 0.f;
+#pragma unroll 4
     for (int d = 0; d < D; ++d) {
       float qq[4], kk[4];
 #pragma unroll
@@ -372,6 +386,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
 #pragma unroll
     for (int x = 0; x < CV; ++x) acc[i][x] = 0.f;
   // the state at the piece's begin: sum_d q_i[d] S0[d][c], then times exp(m_begin - M_i)
+#pragma unroll 4
   for (int d = 0; d < D; ++d) {
     float qq[4], sv[CV];
 #pragma unroll
@@ -390,6 +405,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
     for (int x = 0; x < CV; ++x) acc[i][x] *= f;
   }
   const int jmax = min(L, ty * 4 + 4);
+#pragma unroll 4
   for (int j = 0; j < jmax; ++j) {
     float pp[4], vv[CV];
 #pragma unroll
@@ -440,7 +456,7 @@ extern "C" int sx_mlstm_pieces_fit(int D, int Dv) {
 template <typename T>
 static int mlstm_pieces_launch(MlArgs a, MlPieces w, int n_seqs, cudaStream_t stream) {
   const int H = a.H, D = a.D, Dv = a.Dv;
-  int rc = sx_launch(mlstm_gates_kernel, dim3(H, n_seqs), dim3(ML_PIECE), 0, stream, a, w);
+  int rc = sx_launch(mlstm_gates_kernel, dim3(w.P, H, n_seqs), dim3(ML_PIECE), 0, stream, a, w);
   if (rc) return rc;
   const size_t sp = ml_piece_smem(D, Dv), sa = ml_apply_smem(D, Dv);
   if (sp > 48 * 1024) cudaFuncSetAttribute(mlstm_piece_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sp);

@@ -18,8 +18,10 @@
 
 #define MOE_MAX_EXPERTS 1024
 
+#define MOE_ROUTE_THREADS 512
+
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ wr, int W, int E,
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ wr, int W, int E,
                                                         int top, float scale, float sum_eps, int* __restrict__ ids,
                                                         float* __restrict__ weights) {
   extern __shared__ float sm[];
@@ -28,9 +30,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ x,
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < W; i += 128) xs[i] = to_f32(x[(size_t)t * W + i]);
+  for (int i = tid; i < W; i += MOE_ROUTE_THREADS) xs[i] = to_f32(x[(size_t)t * W + i]);
   __syncthreads();
-  for (int e = warp; e < E; e += 4) {
+  for (int e = warp; e < E; e += MOE_ROUTE_THREADS / 32) {
     const float* w = wr + (size_t)e * W;
     float d = 0.f;
     if ((W & 3) == 0 && ((uintptr_t)wr & 15) == 0) {          // 16 bytes a load, four loads on the way
@@ -91,11 +93,11 @@ extern "C" int sx_moe_route(const void* x, const float* wr, int T, int W, int E,
   if (smem > 96 * 1024) return SX_ERR_SIZE;
   if (dt == SX_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(moe_route_kernel<float>, dim3(T), dim3(128), smem, stream, (const float*)x, wr, W, E, top, scale, sum_eps, ids, weights);
+    return sx_launch(moe_route_kernel<float>, dim3(T), dim3(MOE_ROUTE_THREADS), smem, stream, (const float*)x, wr, W, E, top, scale, sum_eps, ids, weights);
   }
   if (dt == SX_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(moe_route_kernel<bf16>, dim3(T), dim3(128), smem, stream, (const bf16*)x, wr, W, E, top, scale, sum_eps, ids, weights);
+    return sx_launch(moe_route_kernel<bf16>, dim3(T), dim3(MOE_ROUTE_THREADS), smem, stream, (const bf16*)x, wr, W, E, top, scale, sum_eps, ids, weights);
   }
   return SX_ERR_DTYPE;
 }
@@ -222,14 +224,15 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
 // warps (2 along the rows x 4 along the columns) owns 64 rows x 128 matrix rows; with GATE_UP these are 64 gate rows
 // and the 64 up rows of the same outputs, so a thread holds gate and up of one place and the activation needs no
 // exchange.  Rows of x (gathered through `order`) and of the expert's matrix come by cp.async, 16 bytes a copy,
-// through a ring of MM_STAGES stages of 32 k each; fragments by ldmatrix from rows padded to 80 bytes.  With a few
+// through a ring of MM_STAGES stages of 64 k each (128 bytes of a row a stage); fragments by ldmatrix from rows padded
+// to 144 bytes.  With a few
 // rows per expert (single-token steps) a block still streams its 128 matrix rows once: the kernel is then bound by
 // the experts' weights, which each active expert's blocks read exactly once.  K % 8 == 0.
 // ---------------------------------------------------------------------------------------------------------------
 #define MM_BM 64
 #define MM_BN 128
-#define MM_BK 32
-#define MM_LD 40             // elements of a staged row (32 + 8 of padding)
+#define MM_BK 64
+#define MM_LD 72             // elements of a staged row (64 + 8 of padding)
 #define MM_STAGES 4
 
 __device__ __forceinline__ void mm_cp16(void* smem, const void* gmem, bool ok) {
@@ -278,15 +281,21 @@ __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A
   constexpr int NOUT = GATE_UP ? MM_BN / 2 : MM_BN;                 // output columns of a block
   const int n0 = blockIdx.x * NOUT;
   const bf16* We = Wt + (size_t)e * (GATE_UP ? 2 : 1) * N * K;
-  // what this thread copies each stage: one 16-byte piece of x and two of the matrix
-  const int a_row = tid >> 2, a_ch = tid & 3;
-  const bf16* a_src = A + (size_t)max(src[a_row], 0) * K + a_ch * 8;
-  const bool a_ok = src[a_row] >= 0;
-  const bf16* w_src[2];
-  bool w_ok[2];
+  // what this thread copies each stage: 16-byte piece a_ch of two rows of x and of four rows of the matrix
+  const int a_ch = tid & 7;
+  const bf16* a_src[2];
+  bool a_ok[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int r = (tid + i * 256) >> 2;                              // row of the staged tile
+    const int r = (tid + i * 256) >> 3;
+    a_ok[i] = src[r] >= 0;
+    a_src[i] = A + (size_t)max(src[r], 0) * K + a_ch * 8;
+  }
+  const bf16* w_src[4];
+  bool w_ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (tid + i * 256) >> 3;                              // row of the staged tile
     int n;                                                           // row of the expert's matrix
     bool ok;
     if (GATE_UP) { const int c = n0 + (r & 63); ok = c < N; n = (r < 64 ? 0 : N) + c; }
@@ -298,10 +307,12 @@ __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A
   auto load = [&](int kt, int stage) {
     const int k0 = kt * MM_BK;
     const bool kin = k0 + a_ch * 8 < K;
-    mm_cp16(As + ((size_t)stage * MM_BM + a_row) * MM_LD + a_ch * 8, a_src + k0, a_ok && kin);
 #pragma unroll
     for (int i = 0; i < 2; ++i)
-      mm_cp16(Ws + ((size_t)stage * MM_BN + ((tid + i * 256) >> 2)) * MM_LD + a_ch * 8, w_src[i] + k0, w_ok[i] && kin);
+      mm_cp16(As + ((size_t)stage * MM_BM + ((tid + i * 256) >> 3)) * MM_LD + a_ch * 8, a_src[i] + k0, a_ok[i] && kin);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      mm_cp16(Ws + ((size_t)stage * MM_BN + ((tid + i * 256) >> 3)) * MM_LD + a_ch * 8, w_src[i] + k0, w_ok[i] && kin);
   };
 #pragma unroll
   for (int s = 0; s < MM_STAGES - 1; ++s) {
