@@ -413,6 +413,21 @@ __global__ void latent_expand_kernel(const T* __restrict__ kv, const T* __restri
   const int page = table[(size_t)seq_of_token[t] * maxp + (pos >> 6)];
   const int E = D + Dr, row = pos & 63;
   const T* src = kv + (size_t)t * (H * D + H * Dv);
+  constexpr int VEC = 16 / (int)sizeof(T);
+  if (D % VEC == 0 && Dr % VEC == 0 && Dv % VEC == 0 && (((uintptr_t)kv | (uintptr_t)kr | (uintptr_t)kp | (uintptr_t)vp) & 15) == 0) {
+    const int e4 = E / VEC, d4 = D / VEC, v4 = Dv / VEC;               // 16-byte pieces
+    for (int i = threadIdx.x; i < H * e4; i += blockDim.x) {
+      const int h = i / e4, e = i % e4;
+      const uint4 v = e < d4 ? reinterpret_cast<const uint4*>(src + h * D)[e]
+                             : reinterpret_cast<const uint4*>(kr + (size_t)t * Dr)[e - d4];
+      reinterpret_cast<uint4*>(kp + (((size_t)page * H + h) * SX_PAGE + row) * E)[e] = v;
+    }
+    for (int i = threadIdx.x; i < H * v4; i += blockDim.x) {
+      const int h = i / v4, e = i % v4;
+      reinterpret_cast<uint4*>(vp + (((size_t)page * H + h) * SX_PAGE + row) * Dv)[e] = reinterpret_cast<const uint4*>(src + H * D + h * Dv)[e];
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H * E; i += blockDim.x) {
     const int h = i / E, e = i % E;
     kp[(((size_t)page * H + h) * SX_PAGE + row) * E + e] = e < D ? src[h * D + e] : kr[(size_t)t * Dr + (e - D)];
@@ -449,6 +464,20 @@ __global__ void head_gate_kernel(T* __restrict__ y, const T* __restrict__ proj, 
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  if (Dv % VEC == 0 && ((uintptr_t)y & 15) == 0) {
+    const int v4 = Dv / VEC;
+    for (int i = threadIdx.x; i < H * v4; i += blockDim.x) {
+      const float g = 1.f / (1.f + expf(-to_f32(proj[(size_t)t * row + col + i / v4])));
+      uint4* p = reinterpret_cast<uint4*>(y + (size_t)t * H * Dv) + i;
+      uint4 v = *p;
+      T* x = reinterpret_cast<T*>(&v);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) x[k] = from_f32<T>(to_f32(x[k]) * g);
+      *p = v;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H * Dv; i += blockDim.x) {
     const float g = 1.f / (1.f + expf(-to_f32(proj[(size_t)t * row + col + i / Dv])));
     y[(size_t)t * H * Dv + i] = from_f32<T>(to_f32(y[(size_t)t * H * Dv + i]) * g);
