@@ -154,17 +154,20 @@ extern "C" int sx_latent_query(const void* q, const void* wuk, int H, int D, int
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// RI: elements of the weighted latent a lane owns (R <= 32 * RI).  The grid's z axis splits the window's key tiles
-// among blocks (single-token steps of few sequences would otherwise fill a fraction of the SMs); every block writes its
-// weighted sum without the division, out [T, H, splits, R], and its maximum and sum of weights, ml [T, H, splits, 2];
-// the output kernel merges them.
-template <typename T, int RI>
+// RI: elements of the weighted latent a lane owns (R <= 32 * RI; with V4, R <= 128 * RI / 4).  The grid's z axis splits the
+// window's key tiles among blocks (single-token steps of few sequences would otherwise fill a fraction of the SMs); every
+// block writes its weighted sum without the division, out [T, H, splits, R], and its maximum and sum of weights,
+// ml [T, H, splits, 2]; the output kernel merges them.
+// V4 (R and Dr multiples of 4): staged rows are padded by four floats, so that rows stay 16-byte aligned and the lanes'
+// 16-byte loads of different rows fall on different banks; scores take four elements of q and of the key a load, and a
+// lane owns the latent's elements 4 lane .. 4 lane + 3 (+ 128, ...), which it reads and writes 16 bytes at a time.
+template <typename T, int RI, bool V4>
 __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
     const float* __restrict__ qa, const T* __restrict__ k_pages, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int maxp, int H, int R, int Dr, float scale,
     int window, float* __restrict__ out, float* __restrict__ ml) {
-  extern __shared__ float sm[];
-  const int E = R + Dr, ES = E + 1;        // a staged row is padded by one float: lanes read different rows
+  extern __shared__ __align__(16) float sm[];
+  const int E = R + Dr, ES = V4 ? E + 4 : E + 1;   // lanes read different rows: the padding spreads them over the banks
   float* ks = sm;                          // LT_KEYS * ES
   float* qs = ks + LT_KEYS * ES;           // LT_HEADS * E
   pdl_wait();
@@ -200,8 +203,14 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
         for (int c = lane; c < E / VEC; c += 32) {
           const uint4 v = src[c];
           const T* x = reinterpret_cast<const T*>(&v);
+          if (V4) {
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) dst[c * VEC + i] = to_f32(x[i]);
+            for (int i = 0; i < VEC; i += 4)
+              *reinterpret_cast<float4*>(dst + c * VEC + i) = make_float4(to_f32(x[i]), to_f32(x[i + 1]), to_f32(x[i + 2]), to_f32(x[i + 3]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) dst[c * VEC + i] = to_f32(x[i]);
+          }
         }
       }
     } else {
@@ -217,14 +226,22 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
     if (lane < nk) {
       const float* kr = ks + lane * ES;
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;      // four sums side by side: the chain of one would wait on itself
-      int e = 0;
-      for (; e + 3 < E; e += 4) {
-        d0 = fmaf(qh[e], kr[e], d0);
-        d1 = fmaf(qh[e + 1], kr[e + 1], d1);
-        d2 = fmaf(qh[e + 2], kr[e + 2], d2);
-        d3 = fmaf(qh[e + 3], kr[e + 3], d3);
+      if (V4) {
+#pragma unroll 4
+        for (int e = 0; e < E; e += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qh + e), k4 = *reinterpret_cast<const float4*>(kr + e);
+          d0 = fmaf(q4.x, k4.x, d0); d1 = fmaf(q4.y, k4.y, d1); d2 = fmaf(q4.z, k4.z, d2); d3 = fmaf(q4.w, k4.w, d3);
+        }
+      } else {
+        int e = 0;
+        for (; e + 3 < E; e += 4) {
+          d0 = fmaf(qh[e], kr[e], d0);
+          d1 = fmaf(qh[e + 1], kr[e + 1], d1);
+          d2 = fmaf(qh[e + 2], kr[e + 2], d2);
+          d3 = fmaf(qh[e + 3], kr[e + 3], d3);
+        }
+        for (; e < E; ++e) d0 = fmaf(qh[e], kr[e], d0);
       }
-      for (; e < E; ++e) d0 = fmaf(qh[e], kr[e], d0);
       s = ((d0 + d1) + (d2 + d3)) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -237,19 +254,39 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
     for (int jj = 0; jj < nk; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const float* kr = ks + jj * ES;
+      if (V4) {
 #pragma unroll
-      for (int i = 0; i < RI; ++i) {
-        const int r = lane + 32 * i;
-        if (r < R) acc[i] = fmaf(pj, kr[r], acc[i]);
+        for (int i = 0; i < RI / 4; ++i) {
+          const int r = lane * 4 + 128 * i;
+          if (r < R) {
+            const float4 c4 = *reinterpret_cast<const float4*>(kr + r);
+            acc[4 * i] = fmaf(pj, c4.x, acc[4 * i]); acc[4 * i + 1] = fmaf(pj, c4.y, acc[4 * i + 1]);
+            acc[4 * i + 2] = fmaf(pj, c4.z, acc[4 * i + 2]); acc[4 * i + 3] = fmaf(pj, c4.w, acc[4 * i + 3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < RI; ++i) {
+          const int r = lane + 32 * i;
+          if (r < R) acc[i] = fmaf(pj, kr[r], acc[i]);
+        }
       }
     }
   }
   if (live) {
     float* o = out + (((size_t)t * H + h) * splits + split) * R;
+    if (V4) {
 #pragma unroll
-    for (int i = 0; i < RI; ++i) {
-      const int r = lane + 32 * i;
-      if (r < R) o[r] = acc[i];
+      for (int i = 0; i < RI / 4; ++i) {
+        const int r = lane * 4 + 128 * i;
+        if (r < R) *reinterpret_cast<float4*>(o + r) = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < RI; ++i) {
+        const int r = lane + 32 * i;
+        if (r < R) o[r] = acc[i];
+      }
     }
     if (lane == 0) {
       ml[(((size_t)t * H + h) * splits + split) * 2] = m;
@@ -258,29 +295,37 @@ __global__ void __launch_bounds__(LT_HEADS * 32) latent_attn_kernel(
   }
 }
 
-template <typename T, int RI>
+template <typename T, int RI, bool V4>
 static int latent_attn_launch(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
                               const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out,
                               float* ml, int splits, int T_, cudaStream_t stream) {
-  const size_t smem = (size_t)(LT_KEYS * (R + Dr + 1) + LT_HEADS * (R + Dr)) * sizeof(float);
+  const size_t smem = (size_t)(LT_KEYS * (R + Dr + (V4 ? 4 : 1)) + LT_HEADS * (R + Dr)) * sizeof(float);
   if (smem > 200 * 1024) return SX_ERR_SIZE;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<T, RI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<T, RI, V4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(T_, (H + LT_HEADS - 1) / LT_HEADS, splits);
-  return sx_launch(latent_attn_kernel<T, RI>, grid, dim3(LT_HEADS * 32), smem, stream, qa, (const T*)k_pages, positions, seq_of_token,
-                   block_table, maxp, H, R, Dr, scale, window, out, ml);
+  return sx_launch(latent_attn_kernel<T, RI, V4>, grid, dim3(LT_HEADS * 32), smem, stream, qa, (const T*)k_pages, positions,
+                   seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, ml);
 }
 
 template <typename T>
 static int latent_attn_any(const float* qa, const void* k_pages, const int* positions, const int* seq_of_token,
                            const int* block_table, int maxp, int H, int R, int Dr, float scale, int window, float* out, float* ml,
                            int splits, int T_, cudaStream_t stream) {
-#define LT_CASE(RI) return latent_attn_launch<T, RI>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, ml, splits, T_, stream)
-  if (R <= 32 * 2) LT_CASE(2);
-  if (R <= 32 * 4) LT_CASE(4);
-  if (R <= 32 * 8) LT_CASE(8);
-  if (R <= 32 * 12) LT_CASE(12);
-  if (R <= 32 * 16) LT_CASE(16);
-  if (R <= 32 * 32) LT_CASE(32);
+#define LT_CASE(RI, V4) return latent_attn_launch<T, RI, V4>(qa, k_pages, positions, seq_of_token, block_table, maxp, H, R, Dr, scale, window, out, ml, splits, T_, stream)
+  if (R % 4 == 0 && Dr % 4 == 0 && (((uintptr_t)qa | (uintptr_t)out) & 15) == 0) {      // a lane owns groups of four elements
+    if (R <= 128) LT_CASE(4, true);
+    if (R <= 256) LT_CASE(8, true);
+    if (R <= 384) LT_CASE(12, true);
+    if (R <= 512) LT_CASE(16, true);
+    if (R <= 1024) LT_CASE(32, true);
+    return SX_ERR_SIZE;
+  }
+  if (R <= 32 * 2) LT_CASE(2, false);
+  if (R <= 32 * 4) LT_CASE(4, false);
+  if (R <= 32 * 8) LT_CASE(8, false);
+  if (R <= 32 * 12) LT_CASE(12, false);
+  if (R <= 32 * 16) LT_CASE(16, false);
+  if (R <= 32 * 32) LT_CASE(32, false);
 #undef LT_CASE
   return SX_ERR_SIZE;
 }

@@ -43,7 +43,7 @@ PA_INIT = dict(seed=5, std_matrix=0.12, std_embedding=0.5, std_gain=0.2, std_bia
 PB = dict(architecture="Pidutar", vocab=77, width=64, norm=dict(eps=1e-6), embedding=dict(scale=1.0), residual_mult=1.0,
           logit_scale=1.0,
           layers=[_mem(4, 8, 8, 9.0, _moe(32, 4, 2, 1.0)),
-                  _mem(2, 24, 12, 12.0, _moe(32, 6, 1, 3.0)),
+                  _mem(2, 24, 12, 11.0, _moe(32, 6, 1, 3.0)),
                   _lat(9, 8, 12, 8, 40, 36, 0.2, 65, (4, 5.0e5), _moe(48, 3, 2, 1.0)),
                   _lat(1, 16, 4, 32, 16, 24, 0.35, 1, (4, 100.0), None),
                   _lat(2, 8, 12, 16, 24, 36, 0.3, 130, (4, 5.0e5), _moe(16, 8, 4, 0.5), kv_from=2)])
@@ -53,20 +53,20 @@ PB_INIT = dict(seed=9, std_matrix=0.1, std_embedding=0.7, std_gain=0.15, std_bia
 # its reader, no rotation at all in another pair, rot_dim 0 is not used but dim 0 is: a head of rotated elements alone
 PF = dict(architecture="Pidutar", vocab=256, width=128, norm=dict(eps=1e-5), embedding=dict(scale=4.0), residual_mult=0.25,
           logit_scale=0.125,
-          layers=[_lat(4, 32, 32, 32, 64, 64, 0.125, None, (32, 1.0e6), _moe(64, 8, 2, 2.0)),
-                  _mem(2, 32, 64, 10.0, _moe(64, 8, 2, 2.0)),
-                  _lat(4, 32, 32, 32, 64, 64, 0.125, 100, (32, 1.0e6), _moe(64, 8, 2, 2.0), kv_from=0),
+          layers=[_lat(4, 32, 32, 32, 64, 64, 0.11, None, (32, 2.0e5), _moe(64, 8, 2, 1.5)),
+                  _mem(2, 32, 64, 10.0, _moe(64, 8, 2, 1.5)),
+                  _lat(4, 32, 32, 32, 64, 64, 0.11, 100, (32, 2.0e5), _moe(64, 8, 2, 1.5), kv_from=0),
                   _lat(2, 0, 64, 64, 32, 96, 0.2, 40, None, _moe(32, 16, 4, 1.0)),
                   _mem(4, 64, 32, 8.0, _moe(96, 4, 3, 1.0))])
 PF_INIT = dict(seed=13, std_matrix=0.08, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
 
 # head sizes that the tensor-core attention over per-head keys and values takes (dim + rot_dim = vdim = 64 and 128):
 # whole prompts of 256 tokens and more run that form in bfloat16; a reader with wider heads than its owner and no window
-PT = dict(architecture="Pidutar", vocab=160, width=128, norm=dict(eps=1e-5), embedding=dict(scale=3.0), residual_mult=0.3,
-          logit_scale=0.25,
-          layers=[_lat(4, 32, 32, 64, 64, 64, 0.125, 100, (32, 1.0e6), _moe(64, 4, 2, 2.0)),
-                  _mem(2, 32, 32, 10.0, _moe(64, 4, 2, 2.0)),
-                  _lat(2, 96, 32, 128, 32, 64, 0.09, None, (32, 1.0e6), _moe(64, 4, 2, 2.0), kv_from=0),
+PT = dict(architecture="Pidutar", vocab=160, width=128, norm=dict(eps=1e-5), embedding=dict(scale=2.0), residual_mult=0.35,
+          logit_scale=0.5,
+          layers=[_lat(4, 32, 32, 64, 64, 64, 0.13, 100, (32, 3.0e5), _moe(64, 4, 2, 1.25)),
+                  _mem(2, 32, 32, 10.0, _moe(64, 4, 2, 1.25)),
+                  _lat(2, 96, 32, 128, 32, 64, 0.09, None, (32, 3.0e5), _moe(64, 4, 2, 1.25), kv_from=0),
                   _lat(3, 48, 16, 64, 48, 40, 0.12, 64, (8, 1.0e4), None)])
 PT_INIT = dict(seed=17, std_matrix=0.08, std_embedding=0.4, std_gain=0.1, std_bias=0.3)
 
