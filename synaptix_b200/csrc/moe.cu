@@ -224,16 +224,24 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
 // warps (2 along the rows x 4 along the columns) owns 64 rows x 128 matrix rows; with GATE_UP these are 64 gate rows
 // and the 64 up rows of the same outputs, so a thread holds gate and up of one place and the activation needs no
 // exchange.  Rows of x (gathered through `order`) and of the expert's matrix come by cp.async, 16 bytes a copy,
-// through a ring of MM_STAGES stages of 64 k each (128 bytes of a row a stage); fragments by ldmatrix from rows padded
+// through a ring of stages of 64 k each (128 bytes of a row a stage); fragments by ldmatrix from rows padded
 // to 144 bytes.  With a few
 // rows per expert (single-token steps) a block still streams its 128 matrix rows once: the kernel is then bound by
 // the experts' weights, which each active expert's blocks read exactly once.  K % 8 == 0.
 // ---------------------------------------------------------------------------------------------------------------
-#define MM_BM 64
 #define MM_BN 128
 #define MM_BK 64
 #define MM_LD 72             // elements of a staged row (64 + 8 of padding)
-#define MM_STAGES 4
+// rows a block (BM) and stages of its ring: 64 rows with 4 stages (two blocks an SM), or, for steps whose experts get
+// a handful of rows each, 16 rows with 8 stages: seven stages of 18 KB of weights on the way per SM
+template <int BM> struct MmShape {
+  static constexpr int STAGES = BM == 64 ? 4 : 8;
+  static constexpr int WARPS_M = BM == 64 ? 2 : 1;
+  static constexpr int WARPS_N = 8 / WARPS_M;
+  static constexpr int MI = BM / (16 * WARPS_M);                    // m16 tiles a warp
+  static constexpr int NT = MM_BN / WARPS_N / 8;                     // n8 tiles a warp: 4 or 2
+  static constexpr size_t SMEM = (size_t)STAGES * (BM + MM_BN) * MM_LD * sizeof(bf16);
+};
 
 __device__ __forceinline__ void mm_cp16(void* smem, const void* gmem, bool ok) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem);
@@ -251,14 +259,16 @@ __device__ __forceinline__ void mm_mma(float* c, const uint32_t* a, uint32_t b0,
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename TC, bool GATE_UP>
+template <typename TC, bool GATE_UP, int BM>
 __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ Wt, TC* __restrict__ C,
                                                       const int* __restrict__ offsets, const int* __restrict__ order,
                                                       int E, int N, int K, int top) {
+  using Sh = MmShape<BM>;
+  constexpr int STAGES = Sh::STAGES, MI = Sh::MI, NT = Sh::NT;
   extern __shared__ __align__(16) unsigned char mm_smem[];
-  bf16* As = (bf16*)mm_smem;                                        // MM_STAGES * MM_BM * MM_LD
-  bf16* Ws = As + MM_STAGES * MM_BM * MM_LD;                        // MM_STAGES * MM_BN * MM_LD
-  __shared__ int src[MM_BM];
+  bf16* As = (bf16*)mm_smem;                                        // STAGES * BM * MM_LD
+  bf16* Ws = As + STAGES * BM * MM_LD;                              // STAGES * MM_BN * MM_LD
+  __shared__ int src[BM];
   __shared__ int which[3];
   pdl_wait();
   pdl_trigger();
@@ -267,29 +277,30 @@ __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A
     int tile = blockIdx.y, e = 0, r0 = -1;
     for (; e < E; ++e) {
       const int n_e = offsets[e + 1] - offsets[e];
-      const int tiles = (n_e + MM_BM - 1) / MM_BM;
-      if (tile < tiles) { r0 = offsets[e] + tile * MM_BM; break; }
+      const int tiles = (n_e + BM - 1) / BM;
+      if (tile < tiles) { r0 = offsets[e] + tile * BM; break; }
       tile -= tiles;
     }
-    which[0] = e; which[1] = r0; which[2] = r0 >= 0 ? min(MM_BM, offsets[e + 1] - r0) : 0;
+    which[0] = e; which[1] = r0; which[2] = r0 >= 0 ? min(BM, offsets[e + 1] - r0) : 0;
   }
   __syncthreads();
   const int e = which[0], r0 = which[1], nr = which[2];
   if (r0 < 0) return;
-  if (tid < MM_BM) src[tid] = tid < nr ? (GATE_UP ? order[r0 + tid] / top : r0 + tid) : -1;
+  if (tid < BM) src[tid] = tid < nr ? (GATE_UP ? order[r0 + tid] / top : r0 + tid) : -1;
   __syncthreads();
   constexpr int NOUT = GATE_UP ? MM_BN / 2 : MM_BN;                 // output columns of a block
   const int n0 = blockIdx.x * NOUT;
   const bf16* We = Wt + (size_t)e * (GATE_UP ? 2 : 1) * N * K;
-  // what this thread copies each stage: 16-byte piece a_ch of two rows of x and of four rows of the matrix
+  // what this thread copies each stage: 16-byte piece a_ch of (up to) two rows of x and of four rows of the matrix
+  constexpr int A_COPIES = (BM * 8 + 255) / 256;
   const int a_ch = tid & 7;
-  const bf16* a_src[2];
-  bool a_ok[2];
+  const bf16* a_src[A_COPIES];
+  bool a_ok[A_COPIES];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < A_COPIES; ++i) {
     const int r = (tid + i * 256) >> 3;
-    a_ok[i] = src[r] >= 0;
-    a_src[i] = A + (size_t)max(src[r], 0) * K + a_ch * 8;
+    a_ok[i] = r < BM && src[r < BM ? r : 0] >= 0;
+    a_src[i] = A + (size_t)(a_ok[i] ? src[r] : 0) * K + a_ch * 8;
   }
   const bf16* w_src[4];
   bool w_ok[4];
@@ -308,47 +319,54 @@ __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A
     const int k0 = kt * MM_BK;
     const bool kin = k0 + a_ch * 8 < K;
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
-      mm_cp16(As + ((size_t)stage * MM_BM + ((tid + i * 256) >> 3)) * MM_LD + a_ch * 8, a_src[i] + k0, a_ok[i] && kin);
+    for (int i = 0; i < A_COPIES; ++i) {
+      const int r = (tid + i * 256) >> 3;
+      if (r < BM) mm_cp16(As + ((size_t)stage * BM + r) * MM_LD + a_ch * 8, a_src[i] + k0, a_ok[i] && kin);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       mm_cp16(Ws + ((size_t)stage * MM_BN + ((tid + i * 256) >> 3)) * MM_LD + a_ch * 8, w_src[i] + k0, w_ok[i] && kin);
   };
 #pragma unroll
-  for (int s = 0; s < MM_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < nk) load(s, s);
     mm_commit();
   }
-  const int wm = warp >> 2, wn = warp & 3;                           // 2 x 4 warps; a warp: 32 rows x 4 n8 tiles
-  float acc[2][4][4];
+  const int wm = warp / Sh::WARPS_N, wn = warp % Sh::WARPS_N;       // a warp: MI m16 tiles x NT n8 tiles
+  float acc[MI][NT][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < NT; ++j)
 #pragma unroll
       for (int x = 0; x < 4; ++x) acc[i][j][x] = 0.f;
   for (int kt = 0; kt < nk; ++kt) {
-    mm_wait<MM_STAGES - 2>();
+    mm_wait<STAGES - 2>();
     __syncthreads();                                                 // stage kt has landed; stage kt - 1 is read out
-    if (kt + MM_STAGES - 1 < nk) load(kt + MM_STAGES - 1, (kt + MM_STAGES - 1) % MM_STAGES);
+    if (kt + STAGES - 1 < nk) load(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     mm_commit();
-    const bf16* as = As + (size_t)(kt % MM_STAGES) * MM_BM * MM_LD;
-    const bf16* ws = Ws + (size_t)(kt % MM_STAGES) * MM_BN * MM_LD;
+    const bf16* as = As + (size_t)(kt % STAGES) * BM * MM_LD;
+    const bf16* ws = Ws + (size_t)(kt % STAGES) * MM_BN * MM_LD;
 #pragma unroll
     for (int kk = 0; kk < MM_BK / 16; ++kk) {
-      uint32_t af[2][4];
+      uint32_t af[MI][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
+      for (int mi = 0; mi < MI; ++mi)
         mm_ldsm4(af[mi][0], af[mi][1], af[mi][2], af[mi][3],
-                 as + (size_t)(wm * 32 + mi * 16 + (lane & 15)) * MM_LD + kk * 16 + (lane >> 4) * 8);
+                 as + (size_t)(wm * MI * 16 + mi * 16 + (lane & 15)) * MM_LD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
-      for (int pair = 0; pair < 2; ++pair) {                         // two n8 tiles a load
-        // GATE_UP: pair 0 = this warp's 16 gate rows (staged rows wn * 16 ..), pair 1 = its 16 up rows (64 + wn * 16 ..)
-        const int nb = GATE_UP ? pair * 64 + wn * 16 : wn * 32 + pair * 16;
+      for (int pair = 0; pair < NT / 2; ++pair) {                    // two n8 tiles a load
+        // the staged row of this lane's address.  GATE_UP: a warp's gate tiles first, then its up tiles (staged rows
+        // 64 ..): with four tiles a warp pair 0 = gate, pair 1 = up; with two the one load takes a gate and an up tile
+        const int sub = lane >> 4;
+        int nb;
+        if (!GATE_UP) nb = wn * NT * 8 + pair * 16 + sub * 8;
+        else if (NT == 4) nb = pair * 64 + wn * 16 + sub * 8;
+        else nb = sub * 64 + wn * 8;
         uint32_t b0, b1, b2, b3;
-        mm_ldsm4(b0, b1, b2, b3, ws + (size_t)(nb + (lane & 7) + (lane >> 4) * 8) * MM_LD + kk * 16 + ((lane >> 3) & 1) * 8);
+        mm_ldsm4(b0, b1, b2, b3, ws + (size_t)(nb + (lane & 7)) * MM_LD + kk * 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
-        for (int mi = 0; mi < 2; ++mi) {
+        for (int mi = 0; mi < MI; ++mi) {
           mm_mma(acc[mi][pair * 2], af[mi], b0, b1);
           mm_mma(acc[mi][pair * 2 + 1], af[mi], b2, b3);
         }
@@ -358,47 +376,52 @@ __global__ void __launch_bounds__(256) moe_mma_kernel(const bf16* __restrict__ A
   mm_wait<0>();
   const int row_in = lane >> 2, col_in = (lane & 3) * 2;
 #pragma unroll
-  for (int mi = 0; mi < 2; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int r = wm * 32 + mi * 16 + half * 8 + row_in;
+      const int r = wm * MI * 16 + mi * 16 + half * 8 + row_in;
       if (r >= nr) continue;
       TC* crow = C + (size_t)(r0 + r) * N;
       if (GATE_UP) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < NT / 2; ++j)
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const int n = n0 + wn * 16 + j * 8 + col_in + x;
-            if (n < N) crow[n] = from_f32<TC>(moe_silu(acc[mi][j][half * 2 + x]) * acc[mi][2 + j][half * 2 + x]);
+            const int n = n0 + wn * (NT / 2) * 8 + j * 8 + col_in + x;
+            if (n < N) crow[n] = from_f32<TC>(moe_silu(acc[mi][j][half * 2 + x]) * acc[mi][NT / 2 + j][half * 2 + x]);
           }
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < NT; ++j)
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const int n = n0 + wn * 32 + j * 8 + col_in + x;
+            const int n = n0 + wn * NT * 8 + j * 8 + col_in + x;
             if (n < N) crow[n] = from_f32<TC>(acc[mi][j][half * 2 + x]);
           }
       }
     }
 }
 
-template <typename TC, bool GATE_UP>
-static int moe_mma_launch(const void* A, const void* Wt, void* C, const int* offsets, const int* order, int tiles, int E, int N,
+template <typename TC, bool GATE_UP, int BM>
+static int moe_mma_launch(const void* A, const void* Wt, void* C, const int* offsets, const int* order, int rows, int E, int N,
                           int K, int top, cudaStream_t stream) {
-  const size_t smem = (size_t)MM_STAGES * (MM_BM + MM_BN) * MM_LD * sizeof(bf16);
+  const size_t smem = MmShape<BM>::SMEM;
   static bool set = false;
   if (!set) {
-    cudaError_t err = cudaFuncSetAttribute(moe_mma_kernel<TC, GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(moe_mma_kernel<TC, GATE_UP, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     set = true;
   }
+  const int tiles = (rows + BM - 1) / BM + (E < rows ? E : rows);
+  if (tiles > 65535) return SX_ERR_SIZE;
   const int nout = GATE_UP ? MM_BN / 2 : MM_BN;
   dim3 grid((N + nout - 1) / nout, tiles);
-  return sx_launch(moe_mma_kernel<TC, GATE_UP>, grid, dim3(256), smem, stream, (const bf16*)A, (const bf16*)Wt, (TC*)C, offsets,
+  return sx_launch(moe_mma_kernel<TC, GATE_UP, BM>, grid, dim3(256), smem, stream, (const bf16*)A, (const bf16*)Wt, (TC*)C, offsets,
                    order, E, N, K, top);
 }
+
+// up to this many (token, choice) rows a step, blocks of 16 rows with the deeper ring
+#define MM_FEW_ROWS 64
 
 // rows: T * top; the grid's y axis has room for every expert's last, partly filled tile
 extern "C" int sx_moe_gemm(const void* A, const void* Wt, void* C, const int* offsets, const int* order, int rows, int E, int N,
@@ -408,9 +431,13 @@ extern "C" int sx_moe_gemm(const void* A, const void* Wt, void* C, const int* of
   const int tiles = (rows + 63) / 64 + (E < rows ? E : rows);
   if (tiles > 65535) return SX_ERR_SIZE;
   if (a_dt == SX_BF16 && K % 8 == 0 && ((uintptr_t)A | (uintptr_t)Wt) % 16 == 0) {       // the tensor cores
-    if (gate_up && c_dt == SX_BF16) return moe_mma_launch<bf16, true>(A, Wt, C, offsets, order, tiles, E, N, K, top, stream);
-    if (!gate_up && c_dt == SX_F32) return moe_mma_launch<float, false>(A, Wt, C, offsets, order, tiles, E, N, K, top, stream);
-    if (!gate_up && c_dt == SX_BF16) return moe_mma_launch<bf16, false>(A, Wt, C, offsets, order, tiles, E, N, K, top, stream);
+#define MM_GO(TC, GU)                                                                                               \
+  return rows <= MM_FEW_ROWS ? moe_mma_launch<TC, GU, 16>(A, Wt, C, offsets, order, rows, E, N, K, top, stream)    \
+                             : moe_mma_launch<TC, GU, 64>(A, Wt, C, offsets, order, rows, E, N, K, top, stream)
+    if (gate_up && c_dt == SX_BF16) MM_GO(bf16, true);
+    if (!gate_up && c_dt == SX_F32) MM_GO(float, false);
+    if (!gate_up && c_dt == SX_BF16) MM_GO(bf16, false);
+#undef MM_GO
   }
   dim3 grid((N + 63) / 64, tiles);
 #define MOE_GO(TA, TC, GU) return sx_launch(moe_gemm_kernel<TA, TA, TC, GU>, grid, dim3(256), 0, stream, (const TA*)A, (const TA*)Wt, (TC*)C, offsets, order, E, N, K, top)
