@@ -369,6 +369,7 @@ __global__ void __launch_bounds__(LT_THREADS) latent_output_kernel(
     float v = 0.f;
     if (tt < nt) {
       const float* p = ol + ((size_t)(t0 + tt) * H + h) * splits * R + r;
+#pragma unroll 8
       for (int s = 0; s < splits; ++s) v = fmaf(wsp[tt][s], p[(size_t)s * R], v);
     }
     os[i] = v;
