@@ -48,12 +48,14 @@ struct MlArgs {
   int H, D, Dv;
 };
 
+// in_place: the matrix is too large for shared memory and is updated where it lies (every element is read and written
+// by one thread only)
 template <typename T>
-__global__ void __launch_bounds__(ML_THREADS) mlstm_walk_kernel(MlArgs a) {
+__global__ void __launch_bounds__(ML_THREADS) mlstm_walk_kernel(MlArgs a, int in_place) {
   extern __shared__ float sm[];
   const int D = a.D, Dv = a.Dv, H = a.H;
-  float* S = sm;                     // D * Dv
-  float* nn = S + D * Dv;            // D
+  float* S = sm;                     // D * Dv (not with in_place)
+  float* nn = in_place ? sm : S + D * Dv;            // D
   float* q = nn + D;                 // D
   float* k = q + D;                  // D
   float* v = k + D;                  // Dv
@@ -69,7 +71,9 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_walk_kernel(MlArgs a) {
   float* Sg = a.S + ((size_t)slot * H + h) * D * Dv;
   float* ng = a.n + ((size_t)slot * H + h) * D;
   float* mg = a.m + (size_t)slot * H + h;
-  for (int i = tid; i < D * Dv; i += ML_THREADS) S[i] = Sg[i];
+  if (in_place) S = Sg;
+  else
+    for (int i = tid; i < D * Dv; i += ML_THREADS) S[i] = Sg[i];
   for (int i = tid; i < D; i += ML_THREADS) nn[i] = ng[i];
   float m = *mg;
   const T* proj = (const T*)a.proj;
@@ -129,14 +133,15 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_walk_kernel(MlArgs a) {
     }
     __syncthreads();
   }
-  for (int i = tid; i < D * Dv; i += ML_THREADS) Sg[i] = S[i];
+  if (!in_place)
+    for (int i = tid; i < D * Dv; i += ML_THREADS) Sg[i] = S[i];
   for (int i = tid; i < D; i += ML_THREADS) ng[i] = nn[i];
   if (tid == 0) *mg = m;
   (void)sc;
 }
 
-static size_t ml_walk_smem(int D, int Dv) {
-  return (size_t)(D * Dv + 3 * D + Dv + (ML_THREADS / 32) * Dv + Dv) * sizeof(float);
+static size_t ml_walk_smem(int D, int Dv, bool in_place = false) {
+  return (size_t)((in_place ? 0 : D * Dv) + 3 * D + Dv + (ML_THREADS / 32) * Dv + Dv) * sizeof(float);
 }
 
 extern "C" int sx_mlstm_walk_fits(int D, int Dv) { return ml_walk_smem(D, Dv) <= 200 * 1024 ? 1 : 0; }
@@ -492,17 +497,18 @@ extern "C" int sx_mlstm(const void* proj, int row, int q_off, int k_off, int v_o
     if (dt == SX_BF16) return mlstm_pieces_launch<bf16>(a, w, n_seqs, stream);
     return SX_ERR_DTYPE;
   }
-  const size_t smem = ml_walk_smem(D, Dv);
+  const int in_place = ml_walk_smem(D, Dv) > 200 * 1024 ? 1 : 0;
+  const size_t smem = ml_walk_smem(D, Dv, in_place != 0);
   if (smem > 200 * 1024) return SX_ERR_SIZE;
   MlArgs a = {proj, row, q_off, k_off, v_off, g_off, gates, bias, cap, q_scale, eps, den_eps, gain, S, n, m, out,
               cu_seqlens, seq_slots, H, D, Dv};
   if (dt == SX_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_walk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(mlstm_walk_kernel<float>, dim3(H, n_seqs), dim3(ML_THREADS), smem, stream, a);
+    return sx_launch(mlstm_walk_kernel<float>, dim3(H, n_seqs), dim3(ML_THREADS), smem, stream, a, in_place);
   }
   if (dt == SX_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_walk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(mlstm_walk_kernel<bf16>, dim3(H, n_seqs), dim3(ML_THREADS), smem, stream, a);
+    return sx_launch(mlstm_walk_kernel<bf16>, dim3(H, n_seqs), dim3(ML_THREADS), smem, stream, a, in_place);
   }
   return SX_ERR_DTYPE;
 }

@@ -95,7 +95,7 @@ def test_scaled_branches_summed_and_two_norms_of_one_row(width, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,D,Dv,cap", [(3, 8, 12, 6.0), (2, 64, 32, 15.0), (1, 20, 100, 9.0), (1, 128, 128, 12.0)])
+@pytest.mark.parametrize("heads,D,Dv,cap", [(3, 8, 12, 6.0), (2, 64, 32, 15.0), (1, 20, 100, 9.0), (1, 128, 128, 13.0), (1, 260, 200, 8.0)])
 def test_matrix_memory_over_portions(heads, D, Dv, cap, dtype):
     """Portions of many sizes down to single tokens, the three states going on in each sequence's slot; the other slots
     hold NaN.  Gate biases push the forget gate both ways, so that the running maximum is led by either of its arms."""
