@@ -308,8 +308,11 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
   float* qs = sm;                        // ML_PIECE * DS
   float* ks = qs + ML_PIECE * DS;        // ML_PIECE * DS
   float* vs = ks + ML_PIECE * DS;        // ML_PIECE * Dv
-  float* ps = vs + ML_PIECE * Dv;        // ML_PIECE * (ML_PIECE + 1)
-  float* av = ps + ML_PIECE * (ML_PIECE + 1);   // a_j
+  // the weighted scores, ML_PIECE * (ML_PIECE + 1): in the keys' place once the scores are made (the keys are not read
+  // again), where that is large enough: two blocks then fit an SM at head sizes of 128
+  const bool ps_over_keys = D >= ML_PIECE;
+  float* ps = ps_over_keys ? ks : vs + ML_PIECE * Dv;
+  float* av = vs + ML_PIECE * Dv + (ps_over_keys ? 0 : ML_PIECE * (ML_PIECE + 1));   // a_j
   float* bv = av + ML_PIECE;             // b_i
   float* Mv = bv + ML_PIECE;             // M_i = max(m_begin, max_{j<=i} a_j)
   float* dn = Mv + ML_PIECE;             // denominators
@@ -365,6 +368,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
 #pragma unroll
         for (int x = 0; x < 4; ++x) acc[i][x] = fmaf(qq[i], kk[x], acc[i][x]);
     }
+    __syncthreads();             // every thread has read the keys
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = ty * 4 + i;
@@ -450,7 +454,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_apply_kernel(MlArgs a, MlPie
 
 static size_t ml_piece_smem(int D, int Dv) { return (size_t)ML_PIECE * (D + Dv) * sizeof(float); }
 static size_t ml_apply_smem(int D, int Dv) {
-  return (size_t)(2 * ML_PIECE * (D + 1) + ML_PIECE * Dv + ML_PIECE * (ML_PIECE + 1) + 4 * ML_PIECE) * sizeof(float);
+  return (size_t)(2 * ML_PIECE * (D + 1) + ML_PIECE * Dv + (D >= ML_PIECE ? 0 : ML_PIECE * (ML_PIECE + 1)) + 4 * ML_PIECE) * sizeof(float);
 }
 
 extern "C" int sx_mlstm_piece_tokens() { return ML_PIECE; }

@@ -1,6 +1,6 @@
 // A mixture of gated feed-forward experts (sm_100a), float32 and bfloat16; router, softmax and weights are 32-bit.
 //
-//   moe_route_kernel   one block a token: logits z_e = Wr[e] . x in 32-bit (Wr float32, x widened), softmax over ALL
+//   moe_route_kernel   one block a token (four in prompt steps): logits z_e = Wr[e] . x in 32-bit (Wr float32, x widened), softmax over ALL
 //                      experts, the `top` largest scores (ties: the lower index), weights = score / (sum of the chosen
 //                      + sum_eps) * scale  -> ids [T, top], weights [T, top]
 //   moe_sort_kernel    one block: the T * top (token, choice) pairs sorted by expert: offsets [E + 1], order [T * top]
@@ -20,37 +20,55 @@
 
 #define MOE_ROUTE_THREADS 512
 
-template <typename T>
-__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ wr, int W, int E,
-                                                        int top, float scale, float sum_eps, int* __restrict__ ids,
-                                                        float* __restrict__ weights) {
-  extern __shared__ float sm[];
-  float* xs = sm;            // W
-  float* z = sm + W;         // E
+// TB tokens a block: a warp reads an expert's router row once for all of them; warp i then chooses for token i
+template <typename T, int TB>
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n_tokens,
+                                                                       int W, int E, int top, float scale, float sum_eps,
+                                                                       int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ __align__(16) float sm[];
+  float* xs = sm;                 // TB * W
+  float* zs = sm + TB * W;        // TB * E
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < W; i += MOE_ROUTE_THREADS) xs[i] = to_f32(x[(size_t)t * W + i]);
+  const int t0 = blockIdx.x * TB, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nt = min(TB, n_tokens - t0);
+  for (int i = tid; i < TB * W; i += MOE_ROUTE_THREADS) {
+    const int tt = i / W;
+    xs[i] = tt < nt ? to_f32(x[(size_t)t0 * W + i]) : 0.f;
+  }
   __syncthreads();
   for (int e = warp; e < E; e += MOE_ROUTE_THREADS / 32) {
     const float* w = wr + (size_t)e * W;
-    float d = 0.f;
+    float d[TB];
+#pragma unroll
+    for (int tt = 0; tt < TB; ++tt) d[tt] = 0.f;
     if ((W & 3) == 0 && ((uintptr_t)wr & 15) == 0) {          // 16 bytes a load, four loads on the way
-      float d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll 4
       for (int i = lane * 4; i < W; i += 128) {
         const float4 w4 = *reinterpret_cast<const float4*>(w + i);
-        d = fmaf(xs[i], w4.x, d); d1 = fmaf(xs[i + 1], w4.y, d1); d2 = fmaf(xs[i + 2], w4.z, d2); d3 = fmaf(xs[i + 3], w4.w, d3);
+#pragma unroll
+        for (int tt = 0; tt < TB; ++tt) {
+          const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * W + i);
+          d[tt] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, d[tt]))));
+        }
       }
-      d = (d + d1) + (d2 + d3);
     } else {
-      for (int i = lane; i < W; i += 32) d = fmaf(xs[i], w[i], d);
+      for (int i = lane; i < W; i += 32) {
+        const float wi = w[i];
+#pragma unroll
+        for (int tt = 0; tt < TB; ++tt) d[tt] = fmaf(xs[tt * W + i], wi, d[tt]);
+      }
     }
-    d = warp_sum(d);
-    if (lane == 0) z[e] = d;
+#pragma unroll
+    for (int tt = 0; tt < TB; ++tt) {
+      const float v = warp_sum(d[tt]);
+      if (lane == 0) zs[tt * E + e] = v;
+    }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= nt) return;
+  const int t = t0 + warp;
+  float* z = zs + warp * E;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -85,20 +103,28 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const T* _
   for (int j = lane; j < top; j += 32) weights[(size_t)t * top + j] *= f;
 }
 
+template <typename T, int TB>
+static int moe_route_launch(const void* x, const float* wr, int T_, int W, int E, int top, float scale, float sum_eps, int* ids,
+                            float* weights, cudaStream_t stream) {
+  const size_t smem = (size_t)TB * (W + E) * sizeof(float);
+  if (smem > 160 * 1024) return SX_ERR_SIZE;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<T, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return sx_launch(moe_route_kernel<T, TB>, dim3((T_ + TB - 1) / TB), dim3(MOE_ROUTE_THREADS), smem, stream, (const T*)x, wr, T_, W, E,
+                   top, scale, sum_eps, ids, weights);
+}
+
 extern "C" int sx_moe_route(const void* x, const float* wr, int T, int W, int E, int top, float scale, float sum_eps,
                             int* ids, float* weights, int dt, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || W <= 0) return SX_ERR_SIZE;
-  const size_t smem = (size_t)(W + E) * sizeof(float);
-  if (smem > 96 * 1024) return SX_ERR_SIZE;
-  if (dt == SX_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(moe_route_kernel<float>, dim3(T), dim3(MOE_ROUTE_THREADS), smem, stream, (const float*)x, wr, W, E, top, scale, sum_eps, ids, weights);
-  }
-  if (dt == SX_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return sx_launch(moe_route_kernel<bf16>, dim3(T), dim3(MOE_ROUTE_THREADS), smem, stream, (const bf16*)x, wr, W, E, top, scale, sum_eps, ids, weights);
-  }
+  // prompt steps: four tokens a block share every router row they read (where that fits shared memory)
+  const bool four = T >= 256 && (size_t)4 * (W + E) * sizeof(float) <= 160 * 1024;
+  if (dt == SX_F32)
+    return four ? moe_route_launch<float, 4>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream)
+                : moe_route_launch<float, 1>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream);
+  if (dt == SX_BF16)
+    return four ? moe_route_launch<bf16, 4>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream)
+                : moe_route_launch<bf16, 1>(x, wr, T, W, E, top, scale, sum_eps, ids, weights, stream);
   return SX_ERR_DTYPE;
 }
 
