@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(LT_QTHREADS) latent_query_kernel(
     float acc[LT_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < LT_TOKENS; ++tt) acc[tt] = 0.f;
-#pragma unroll 8
+#pragma unroll 16
     for (int d = 0; d < D; ++d) {
       const float w = to_f32(wuk[((size_t)h * D + d) * R + r]);
 #pragma unroll
@@ -364,6 +364,7 @@ __global__ void __launch_bounds__(LT_THREADS) latent_output_kernel(
     }
   }
   __syncthreads();
+#pragma unroll 4                 // the loads of several elements on the way together: they are all the kernel waits for
   for (int i = tid; i < LT_TOKENS * R; i += LT_THREADS) {
     const int tt = i / R, r = i % R;
     float v = 0.f;
@@ -383,7 +384,7 @@ __global__ void __launch_bounds__(LT_THREADS) latent_output_kernel(
     for (int a = 0; a < LT_OUTS; ++a)
 #pragma unroll
       for (int tt = 0; tt < LT_TOKENS; ++tt) acc[a][tt] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
     for (int r = lane; r < R; r += 32) {
       float w[LT_OUTS];
 #pragma unroll
