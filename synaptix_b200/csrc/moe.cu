@@ -258,10 +258,11 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A,
 #define MM_BN 128
 #define MM_BK 64
 #define MM_LD 72             // elements of a staged row (64 + 8 of padding)
-// rows a block (BM) and stages of its ring: 64 rows with 4 stages (two blocks an SM), or, for steps whose experts get
-// a handful of rows each, 16 rows with 8 stages: seven stages of 18 KB of weights on the way per SM
+// rows a block (BM) and stages of its ring: 64 rows with 4 stages, or, for steps whose experts get a handful of rows
+// each, 16 rows with 5 stages; two blocks an SM either way (a gate/up product of 152 blocks then runs in one round of
+// the 148 SMs; with one block an SM the last 4 blocks made a second round), eight stages of 18 KB of weights on the way
 template <int BM> struct MmShape {
-  static constexpr int STAGES = BM == 64 ? 4 : 8;
+  static constexpr int STAGES = BM == 64 ? 4 : 5;
   static constexpr int WARPS_M = BM == 64 ? 2 : 1;
   static constexpr int WARPS_N = 8 / WARPS_M;
   static constexpr int MI = BM / (16 * WARPS_M);                    // m16 tiles a warp
