@@ -24,6 +24,9 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
 ``attn_options_fast``  attention with capped scores, sinks or chunks of positions at head size 32 / 64 / 128 in
                     bfloat16 on the ``mma.sync`` kernels (else the plain kernel)
 ``pdl``             kernels are launched with programmatic dependent launch
+``branch_streams``  single-token steps of a block whose mixer and feed-forward read the same stream: the feed-forward's
+                    kernels run on a second CUDA stream beside the mixer's (inside a captured step: two branches of
+                    the graph), else one after the other
 """
 from __future__ import annotations
 
@@ -43,6 +46,7 @@ class KernelOptions:
     fused_residual: bool = True
     attn_options_fast: bool = True
     pdl: bool = True
+    branch_streams: bool = True
 
 
 OPTIONS = KernelOptions()

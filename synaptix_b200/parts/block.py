@@ -114,10 +114,29 @@ class ConvPreNormBlock(Part):
         return h, self.ffn.forward(y, ctx)
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    """One second stream per device, for a branch that runs beside another."""
+    key = torch.device(device).index or 0
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 class ParallelBlock(Part):
     """``h += mult * (ls1 * mixer(norm1(h)) + ls2 * ffn(norm2(h)))``, both branches of the same ``h``.  ``norm1`` and
     ``norm2`` are RMS norms (their gains may differ, their eps not); ``scale_names`` are the tensors ``ls1`` and
-    ``ls2`` (vectors over the width).  ``norm2`` and ``ffn`` may both be ``None``."""
+    ``ls2`` (vectors over the width).  ``norm2`` and ``ffn`` may both be ``None``.
+
+    The branches do not depend on each other.  In single-token steps, where a layer is a chain of small kernels, the
+    feed-forward runs on a second stream (option ``branch_streams``): it begins behind the norm kernel (an event) and the
+    step's stream waits for its end before anything reads its result; inside a captured step these are two branches of
+    the graph.  What crosses the streams needs no word to the allocator: the feed-forward's input lives until this
+    function returns, by when the step's stream already waits for the feed-forward's end, so its memory is not handed
+    out again before that; the feed-forward's result is read by the next norm on the step's stream, and the second
+    stream does nothing more before an event that is recorded behind such a norm."""
     takes_pending_product = False
 
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], *,
@@ -159,8 +178,20 @@ class ParallelBlock(Part):
             terms = [] if pending is None else [(pending, None)]
         gains = [self.norm1.weight] + ([self.norm2.weight] if self.ffn is not None else [])
         xs = ops.add_scaled_rmsnorm(h, terms, gains, self.norm1.eps, ctx.runtime.dtype)
-        a = self.mixer.forward(xs[0], ctx, cache_view, write_cache)
         if self.ffn is None:
-            return h, ScaledSum([(a, self.s1)])
-        b = self.ffn.forward(xs[1], ctx)
+            return h, ScaledSum([(self.mixer.forward(xs[0], ctx, cache_view, write_cache), self.s1)])
+        if ctx.all_single and ops.OPTIONS.branch_streams and h.is_cuda:
+            main, side = torch.cuda.current_stream(h.device), _side_stream(h.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                b = self.ffn.forward(xs[1], ctx)
+                join = torch.cuda.Event()
+                join.record(side)
+            a = self.mixer.forward(xs[0], ctx, cache_view, write_cache)
+            main.wait_event(join)
+        else:
+            a = self.mixer.forward(xs[0], ctx, cache_view, write_cache)
+            b = self.ffn.forward(xs[1], ctx)
         return h, ScaledSum([(a, self.s1), (b, self.s2)])
